@@ -2,7 +2,8 @@
 // a sequence mixer (windowed attention with kept first tokens, a Mamba-2 state-space mixer, linear attention with a fixed decay per
 // head, or softmax attention over a low-rank latent) and an optional feed-forward (tanh-GELU gated; clamped gated, dense or a routed
 // mixture of experts), inside one of two layer frames: norms before and after every sublayer (FRAME_SANDWICH), or a grouped RMS norm
-// before it with token shift and a depth average of all layer results (FRAME_PRENORM).  Weights are dense f32 / bf16 matrices.  It lives behind the same model object and C ABI as the k-quant transformer engine
+// before it with token shift and a depth average of all layer results (FRAME_PRENORM), or a layer norm with weight and bias on the
+// sublayer's result only, scaled by one factor, with a learned position table on the embedding (FRAME_POSTNORM).  Weights are dense f32 / bf16 matrices.  It lives behind the same model object and C ABI as the k-quant transformer engine
 // (engine.cu): pb200_model_set_tensor / _synth / _finalize / _free, sequence slots, device arg-max — and steps through the ragged
 // batch step (pb200_batch_step) that the scheduler drives; the single-sequence entry points of the k-quant family answer PB200_ENOTSUP.
 //
@@ -47,8 +48,9 @@ extern std::atomic<uint64_t> g_launches;
 namespace pb {
 
 enum : int { MIX_ATTENTION = 0, MIX_MAMBA2 = 1, MIX_DECAY = 2, MIX_LATENT = 3 };
-enum : int { FF_GELU = 0, FF_CLAMPED = 1, FF_MOE = 2 };
-enum : int { FRAME_SANDWICH = 0, FRAME_PRENORM = 1 };
+enum : int { FF_GELU = 0, FF_CLAMPED = 1, FF_MOE = 2, FF_RELU2 = 3 };   // FF_MOE: the expert form is MoeParams::act
+enum : int { FRAME_SANDWICH = 0, FRAME_PRENORM = 1, FRAME_POSTNORM = 2 };
+enum : int { ROUTE_SOFTMAX_TOP = 0, ROUTE_SIGMOID_GROUPS = 1 };
 
 struct DenseW {           // row-major [N][K] in the model's compute type
     void * data = nullptr;
@@ -93,6 +95,14 @@ struct LLayer {
     float shared_limit = 0.f;
     // FRAME_PRENORM
     VecF shift, dwa;
+    // FRAME_POSTNORM: biases of the two norms
+    VecF norm1_bias, norm2_bias;
+    // attention: RMS norm of every query / key head with a weight [dim] all heads share
+    bool qk_norm = false;
+    VecF q_norm, k_norm;
+    // mixture of experts: form of the router; the shared expert's per-token gate vector [width] (ROUTE_SIGMOID_GROUPS)
+    int route = ROUTE_SOFTMAX_TOP;
+    VecF shared_gate;
 };
 
 struct LRun {
@@ -126,6 +136,12 @@ struct LayerList {
     VecF loop_step;
     DenseW embed, head;
     VecF final_norm;
+    // FRAME_POSTNORM
+    DenseW pos_table;         // learned position vectors [max_pos][width], added to the embedding
+    int max_pos = 0;
+    VecF final_norm_bias;
+    float resid_mult = 1.f;   // factor on every normed sublayer result
+    float logit_softcap = 0.f;   // > 0: logits <- cap * tanh(logits / cap)
     // state manager
     int n_ctx = 0, n_seq = 0;
     bool ctx_limited = false;       // some cache holds every position: a sequence cannot outgrow n_ctx
@@ -142,7 +158,7 @@ struct LayerList {
     size_t lat_part_cap = 0;
     // mixture of experts: pairs (token, choice)
     int32_t *moe_idx = nullptr, *moe_perm = nullptr, *moe_row_of = nullptr, *moe_count = nullptr, *moe_start = nullptr, *moe_count_host = nullptr;
-    float *moe_wt = nullptr, *moe_gu = nullptr, *moe_ds = nullptr;
+    float *moe_wt = nullptr, *moe_gu = nullptr, *moe_ds = nullptr, *moe_sg = nullptr;
     void *moe_y = nullptr, *moe_hs = nullptr;
     int32_t *meta_dev = nullptr, *meta_host = nullptr, *greedy_dev = nullptr, *greedy_host = nullptr;
     float * logits_host = nullptr;
@@ -492,11 +508,140 @@ static bool mumizen_resolve(LayerList & ll, const std::string & name, TensorPlac
     return false;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Sapudra: configuration keys and tensor names.  Post-norm layers (layer norm with weight and bias on the sublayer's result, times
+// residual_mult), a learned position table, windowed attention with grouped key / value heads and an RMS norm per query / key head, the
+// squared-ReLU feed-forward, dense or "moe" (sigmoid router with a choice correction and expert groups, gated shared expert), soft-capped logits.
+static int sapudra_configure(const Json & cfg, LayerList & ll, std::string & err) {
+    ll.frame = FRAME_POSTNORM;
+    ll.width = (int) cfg.integer("width", 0);
+    ll.vocab = (int) cfg.integer("vocab", 0);
+    ll.max_pos = (int) cfg.integer("max_positions", 0);
+    ll.resid_mult = (float) cfg.number("residual_mult", 1.0);
+    ll.logit_softcap = (float) cfg.number("logit_softcap", 0.0);
+    ll.logit_scale = 1.f;
+    if (const Json * nrm = cfg.get("norm")) ll.eps = (float) nrm->number("eps", 1e-6);
+    const Json * layers = cfg.get("layers");
+    if (ll.width <= 0 || ll.vocab <= 0 || ll.max_pos <= 0 || !layers || layers->kind != Json::ARR || layers->arr.empty()) { err = "width, vocab, max_positions and layers are required"; return PB200_EINVAL; }
+    for (const Json & jl : layers->arr) {
+        LLayer L;
+        const std::string type = jl.string("type");
+        const Json * mx = jl.get("mixer");
+        if (!mx || mx->kind != Json::OBJ) { err = "layer without mixer"; return PB200_EINVAL; }
+        if (type != "attention") { err = "unknown layer type '" + type + "'"; return PB200_ENOTSUP; }
+        L.kind = MIX_ATTENTION;
+        AttnParams & a = L.att;
+        a.heads = (int) mx->integer("heads", 0);
+        a.kv_heads = (int) mx->integer("kv_heads", a.heads);
+        a.dim = (int) mx->integer("dim", 0);
+        a.vdim = (int) mx->integer("vdim", a.dim);
+        a.scale = (float) mx->number("scale", a.dim > 0 ? 1.0 / std::sqrt((double) a.dim) : 1.0);
+        a.softcap = 0.f;
+        a.gated = 0;
+        a.window = 0;
+        a.keep_first = 0;
+        if (const Json * mk = mx->get("mask"))
+            if (mk->kind == Json::OBJ) a.window = (int) std::min<long long>(mk->integer("size", 0), 1 << 30);
+        L.qk_norm = true;
+        if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads || a.dim <= 0 || a.vdim <= 0 || a.vdim > 512) { err = "attention sizes"; return PB200_EINVAL; }
+        const Json * mlp = jl.get("mlp");
+        if (mlp && mlp->kind == Json::OBJ) {
+            const std::string kind = mlp->string("kind", "dense");
+            if (kind == "dense") {
+                L.ff_kind = FF_RELU2;
+                L.ff = (int) mlp->integer("ff", 0);
+                if (L.ff <= 0) { err = "feed-forward size"; return PB200_EINVAL; }
+            } else if (kind == "moe") {
+                L.ff_kind = FF_MOE;
+                L.route = ROUTE_SIGMOID_GROUPS;
+                MoeParams & p = L.moe;
+                p.act = 1;
+                const Json * ex = mlp->get("expert"), * ro = mlp->get("router"), * sh = mlp->get("shared");
+                if (!ex || ex->kind != Json::OBJ || !ro || ro->kind != Json::OBJ) { err = "moe needs expert and router"; return PB200_EINVAL; }
+                p.ff = (int) ex->integer("ff", 0);
+                L.ff = p.ff;
+                p.experts = (int) ro->integer("experts", 0);
+                p.top = (int) ro->integer("top", 0);
+                p.route_scale = (float) ro->number("scale", 1.0);
+                p.groups = p.keep_groups = 1;
+                if (const Json * gr = ro->get("groups"))
+                    if (gr->kind == Json::OBJ) { p.groups = (int) gr->integer("count", 1); p.keep_groups = (int) gr->integer("keep", p.groups); }
+                if (p.ff <= 0 || p.experts <= 0 || p.top <= 0 || p.top > p.experts || p.top > 32 || p.experts > 4096 || p.groups <= 0 || p.experts % p.groups ||
+                    p.keep_groups <= 0 || p.keep_groups > p.groups || (int64_t) p.keep_groups * (p.experts / p.groups) < p.top) { err = "router sizes"; return PB200_EINVAL; }
+                if (sh && sh->kind == Json::OBJ) {
+                    L.shared_ff = (int) sh->integer("ff", 0);
+                    if (L.shared_ff <= 0) { err = "shared expert size"; return PB200_EINVAL; }
+                }
+            } else {
+                err = "unknown feed-forward kind '" + kind + "'";
+                return PB200_ENOTSUP;
+            }
+        }
+        ll.layers.push_back(std::move(L));
+    }
+    for (int i = 0; i < (int) ll.layers.size(); i++) {
+        LRun r;
+        r.layer = i;
+        ll.runs.push_back(r);
+    }
+    return 0;
+}
+
+static bool sapudra_resolve(LayerList & ll, const std::string & name, TensorPlace & o) {
+    const int64_t W = ll.width;
+    auto mat = [&](DenseW & m, int64_t row0, int64_t rows, int64_t cols, int part) { o.mat = &m; o.row0 = row0; o.rows = rows; o.cols = cols; o.part = part; return true; };
+    auto vec = [&](VecF & v, int64_t n) { o.vec = &v; o.n = n; return true; };
+    if (name == "embed") return mat(ll.embed, 0, ll.vocab, W, 0);
+    if (name == "pos") return mat(ll.pos_table, 0, ll.max_pos, W, 0);
+    if (name == "head") return mat(ll.head, 0, ll.vocab, W, 0);
+    if (name == "final.norm") return vec(ll.final_norm, W);
+    if (name == "final.norm.b") return vec(ll.final_norm_bias, W);
+    int il = -1, used = 0;
+    if (sscanf(name.c_str(), "l%d.%n", &il, &used) != 1 || used <= 0 || il < 0 || il >= (int) ll.layers.size()) return false;
+    LLayer & L = ll.layers[(size_t) il];
+    const std::string w = name.substr((size_t) used);
+    if (w == "norm1") return vec(L.norm1, W);
+    if (w == "norm1.b") return vec(L.norm1_bias, W);
+    const AttnParams & a = L.att;
+    const int64_t QD = (int64_t) a.heads * a.dim, KD = (int64_t) a.kv_heads * a.dim, VD = (int64_t) a.kv_heads * a.vdim;
+    if (w == "mix.q") return mat(L.qkvg, 0, QD, W, 0);
+    if (w == "mix.k") return mat(L.qkvg, QD, KD, W, 1);
+    if (w == "mix.v") return mat(L.qkvg, QD + KD, VD, W, 2);
+    if (w == "mix.q.norm") return vec(L.q_norm, a.dim);
+    if (w == "mix.k.norm") return vec(L.k_norm, a.dim);
+    if (w == "mix.o") return mat(L.out, 0, W, (int64_t) a.heads * a.vdim, 0);
+    if (L.ff <= 0) return false;
+    if (w == "norm2") return vec(L.norm2, W);
+    if (w == "norm2.b") return vec(L.norm2_bias, W);
+    if (w.compare(0, 4, "mlp.") != 0) return false;
+    const std::string f = w.substr(4);
+    if (L.ff_kind == FF_RELU2) {
+        if (f == "up") return mat(L.gateup, 0, L.ff, W, 0);
+        if (f == "down") return mat(L.down, 0, W, L.ff, 0);
+        return false;
+    }
+    if (f == "router") { o.vec = &L.router; o.n = (int64_t) L.moe.experts * W; return true; }
+    if (f == "correction") return vec(L.router_b, L.moe.experts);
+    if (L.shared_ff > 0) {
+        if (f == "shared.up") return mat(L.s_gateup, 0, L.shared_ff, W, 0);
+        if (f == "shared.down") return mat(L.s_down, 0, W, L.shared_ff, 0);
+        if (f == "shared.sg") return vec(L.shared_gate, W);
+    }
+    int e = -1, u2 = 0;
+    if (sscanf(f.c_str(), "e%d.%n", &e, &u2) == 1 && u2 > 0 && e >= 0 && e < L.moe.experts) {
+        const std::string leaf = f.substr((size_t) u2);
+        if (leaf == "up") return mat(L.e_gateup, (int64_t) e * L.moe.ff, L.moe.ff, W, e);
+        if (leaf == "down") return mat(L.e_down, (int64_t) e * W, W, L.moe.ff, e);
+    }
+    return false;
+}
+
 static const ArchEntry g_archs[] = {
     {"llama", ARCH_KQUANT, 0, nullptr, nullptr},
     {"qwen2", ARCH_KQUANT, 2, nullptr, nullptr},
     {"Vamidra", ARCH_LAYERS, 0, vamidra_configure, vamidra_resolve},
     {"Mumizen", ARCH_LAYERS, 0, mumizen_configure, mumizen_resolve},
+    {"Sapudra", ARCH_LAYERS, 0, sapudra_configure, sapudra_resolve},
 };
 int arch_count() { return (int) (sizeof(g_archs) / sizeof(g_archs[0])); }
 const ArchEntry * arch_at(int i) { return (i >= 0 && i < arch_count()) ? &g_archs[i] : nullptr; }
@@ -517,15 +662,18 @@ static void for_each_param(LayerList & ll, FM && fm, FV && fv) {
     fm(ll.embed, (int64_t) ll.vocab, W, 1);
     fm(ll.head, (int64_t) ll.vocab, W, 1);
     fv(ll.final_norm, W, 0);
+    if (ll.frame == FRAME_POSTNORM) { fm(ll.pos_table, (int64_t) ll.max_pos, W, 1); fv(ll.final_norm_bias, W, 1); }
     if (ll.loop_times > 0) { fm(ll.loop_in, W, 2 * W, 1); fv(ll.loop_step, (int64_t) ll.loop_times * W, 1); }
     int il = 0;
     for (LLayer & L : ll.layers) {
         fv(L.norm1, W, 0);
         if (ll.frame == FRAME_SANDWICH) fv(L.norm1b, W, 0);
+        else if (ll.frame == FRAME_POSTNORM) fv(L.norm1_bias, W, 1);
         else { fv(L.shift, W, 5); fv(L.dwa, il + 2, 6); }
         il++;
         if (L.kind == MIX_ATTENTION) {
-            fm(L.qkvg, attn_qkvg_cols(L.att), W, 4);
+            fm(L.qkvg, attn_qkvg_cols(L.att), W, L.att.gated ? 4 : 3);
+            if (L.qk_norm) { fv(L.q_norm, L.att.dim, 0); fv(L.k_norm, L.att.dim, 0); }
             fm(L.out, W, (int64_t) L.att.heads * L.att.vdim, 1);
         } else if (L.kind == MIX_MAMBA2) {
             const Mamba2Params & p = L.ssm;
@@ -553,11 +701,19 @@ static void for_each_param(LayerList & ll, FM && fm, FV && fv) {
         if (L.ff > 0) {
             fv(L.norm2, W, 0);
             if (ll.frame == FRAME_SANDWICH) fv(L.norm2b, W, 0);
+            if (ll.frame == FRAME_POSTNORM) fv(L.norm2_bias, W, 1);
             if (L.ff_kind == FF_MOE) {
-                fm(L.e_gateup, (int64_t) L.moe.experts * 2 * L.moe.ff, W, 2 * L.moe.experts);
+                const int gated = L.moe.act == 0 ? 2 : 1;   // rows per expert: gate | up, or up only
+                fm(L.e_gateup, (int64_t) L.moe.experts * moe_up_rows(L.moe), W, gated * L.moe.experts);
                 fm(L.e_down, (int64_t) L.moe.experts * W, L.moe.ff, L.moe.experts);
                 fv(L.router, (int64_t) L.moe.experts * W, 7); fv(L.router_b, L.moe.experts, 1);
-                if (L.shared_ff > 0) { fm(L.s_gateup, 2 * (int64_t) L.shared_ff, W, 2); fm(L.s_down, W, L.shared_ff, 1); }
+                if (L.shared_ff > 0) {
+                    fm(L.s_gateup, gated * (int64_t) L.shared_ff, W, gated); fm(L.s_down, W, L.shared_ff, 1);
+                    if (L.route == ROUTE_SIGMOID_GROUPS) fv(L.shared_gate, W, 7);
+                }
+            } else if (L.ff_kind == FF_RELU2) {
+                fm(L.gateup, (int64_t) L.ff, W, 1);
+                fm(L.down, W, L.ff, 1);
             } else {
                 fm(L.gateup, 2 * (int64_t) L.ff, W, 2);
                 fm(L.down, W, L.ff, 1);
@@ -855,7 +1011,7 @@ static int ll_reserve(pb200_model * m, int T, int nW, int nE) {
         }
         if (moe_top) {
             const size_t pairs = t * (size_t) moe_top;
-            CK(grab((void **) &ll.moe_idx, pairs * 4)); CK(grab((void **) &ll.moe_wt, pairs * 4));
+            CK(grab((void **) &ll.moe_idx, pairs * 4)); CK(grab((void **) &ll.moe_wt, pairs * 4)); CK(grab((void **) &ll.moe_sg, t * 4));
             CK(grab((void **) &ll.moe_perm, pairs * 4)); CK(grab((void **) &ll.moe_row_of, pairs * 4));
             CK(grab((void **) &ll.moe_count, (size_t) moe_e * 4)); CK(grab((void **) &ll.moe_start, (size_t) moe_e * 4));
             CK(grab(&ll.moe_y, t * (size_t) moe_topff * es)); CK(grab(&ll.moe_hs, pairs * W * es));
@@ -946,7 +1102,8 @@ static int mix_attention(pb200_model * m, const BatchView & b, bool prefill, con
     CK(launch_dense(ct, ll.act, W, L.qkvg.data, W, ll.big, C, T, C, W, nullptr, nullptr, 0, 1.f, st));
     float * kc = sbase, * vc = sbase + (int64_t) a.cache_rows * a.kv_heads * a.dim;
     CAT(CAT_ATTN);
-    CK(launch_attn_kv_store(ll.big, b, a, kc, vc, ll.slot_floats, st));
+    if (L.qk_norm) CK(launch_attn_qknorm_kv_store(ll.big, b, a, L.q_norm.data, L.k_norm.data, ll.eps, kc, vc, ll.slot_floats, st));
+    else CK(launch_attn_kv_store(ll.big, b, a, kc, vc, ll.slot_floats, st));
     if (prefill) CK(launch_attn_window_prefill(ll.big, b, a, ll.act, ct, st));
     else CK(launch_attn_window_decode(ll.big, b, a, kc, vc, ll.slot_floats, ll.act, ct, st));
     CAT(CAT_DENSE);
@@ -1048,30 +1205,65 @@ static int ff_clamped(pb200_model * m, int T, const DenseW & gateup, const Dense
     CAT(CAT_DENSE);
     return launch_dense(ct, ll.act2, ff, down.data, ff, x, W, T, W, ff, nullptr, x, W, 1.f, st);
 }
-static int ff_moe(pb200_model * m, int T, bool prefill, LLayer & L, float * x) {
+// ---- squared-ReLU feed-forward: out[t] = down(max(up(ll.act[t]), 0)^2); ll.act stays as it is ----
+static int ff_relu2(pb200_model * m, int T, const DenseW & up, const DenseW & down, int ff, float * out) {
+    LayerList & ll = *m->ll;
+    cudaStream_t st = m->stream;
+    const int W = ll.width, ct = ll.ctype;
+    CAT(CAT_DENSE);
+    CK(launch_dense(ct, ll.act, W, up.data, W, ll.big, ff, T, ff, W, nullptr, nullptr, 0, 1.f, st));
+    CAT(CAT_ELEM);
+    CK(launch_relu2(ll.big, ll.act2, ct, (int64_t) T * ff, st));
+    CAT(CAT_DENSE);
+    return launch_dense(ct, ll.act2, ff, down.data, ff, out, W, T, W, ff, nullptr, nullptr, 0, 1.f, st);
+}
+// ---- mixture of experts over ll.act.  accumulate: x[t] += shared(h) + sum_k w_k expert_k(h) (the stream itself); otherwise x receives the
+// sublayer's result alone.  The router form and the expert form come from the layer (LLayer::route, MoeParams::act). ----
+static int ff_moe(pb200_model * m, int T, bool prefill, LLayer & L, float * x, bool accumulate) {
     LayerList & ll = *m->ll;
     cudaStream_t st = m->stream;
     const int W = ll.width, ct = ll.ctype;
     const MoeParams & p = L.moe;
     const size_t es = esize(ct);
+    const int UR = moe_up_rows(p);
+    int base = MOE_ADD;
+    const float * xscale = nullptr;
     CAT(CAT_MOE);
-    CK(launch_moe_route(ll.act, ct, L.router.data, L.router_b.data, p, W, ll.moe_idx, ll.moe_wt, T, st));
-    if (L.shared_ff > 0) CK(ff_clamped(m, T, L.s_gateup, L.s_down, L.shared_ff, L.shared_limit, x));
+    if (L.route == ROUTE_SIGMOID_GROUPS) {
+        CK(launch_moe_route_sigmoid(ll.act, ct, L.router.data, L.router_b.data, p, W, L.shared_ff > 0 ? L.shared_gate.data : nullptr, ll.moe_idx, ll.moe_wt, ll.moe_sg, T, st));
+        if (accumulate) return PB200_ENOTSUP;
+        if (L.shared_ff > 0) {   // the shared expert's result waits in x; the kernel that sums the experts multiplies it by the token's gate
+            if (p.act == 1) CK(ff_relu2(m, T, L.s_gateup, L.s_down, L.shared_ff, x));
+            else return PB200_ENOTSUP;
+            base = MOE_SCALE;
+            xscale = ll.moe_sg;
+        } else {
+            base = MOE_SET;
+        }
+    } else {
+        CK(launch_moe_route(ll.act, ct, L.router.data, L.router_b.data, p, W, ll.moe_idx, ll.moe_wt, T, st));
+        if (!accumulate || p.act != 0) return PB200_ENOTSUP;
+        if (L.shared_ff > 0) CK(ff_clamped(m, T, L.s_gateup, L.s_down, L.shared_ff, L.shared_limit, x));
+    }
+    auto activate = [&](int rows) -> int {
+        if (p.act == 1) return launch_relu2(ll.moe_gu, ll.moe_y, ct, (int64_t) rows * p.ff, st);
+        return launch_clamped_glu(ll.moe_gu, ll.moe_y, ct, rows, p.ff, p.limit, st);
+    };
     CAT(CAT_MOE);
     if (!prefill || (int64_t) T * p.top <= 64) {
         CK(launch_moe_gateup_rows(ll.act, ct, L.e_gateup.data, ll.moe_idx, p, W, ll.moe_y, T, st));
-        return launch_moe_down_rows(ll.moe_y, ct, L.e_down.data, ll.moe_idx, ll.moe_wt, p, W, x, T, st);
+        return launch_moe_down_rows(ll.moe_y, ct, L.e_down.data, ll.moe_idx, ll.moe_wt, p, W, x, T, st, base, xscale);
     }
     const int P = T * p.top, E = p.experts;
     CK(launch_moe_sort(ll.moe_idx, p, T, ll.moe_count, ll.moe_start, ll.moe_perm, st));
     CK(launch_moe_gather(ll.act, ct, ll.moe_perm, p.top, W, ll.moe_hs, P, st));
-    if (dense_grouped_ok(ct, 2 * p.ff, W, W, W, (int64_t) 2 * p.ff * W, ll.moe_hs, L.e_gateup.data) &&
+    if (dense_grouped_ok(ct, UR, W, W, W, (int64_t) UR * W, ll.moe_hs, L.e_gateup.data) &&
         dense_grouped_ok(ct, W, p.ff, p.ff, p.ff, (int64_t) W * p.ff, ll.moe_y, L.e_down.data)) {
         // all experts in one launch each way; the row counts never leave the device
-        CK(launch_dense_grouped(ct, ll.moe_hs, W, L.e_gateup.data, W, (int64_t) 2 * p.ff * W, ll.moe_gu, 2 * p.ff, ll.moe_start, ll.moe_count, E, P, 2 * p.ff, W, st));
-        CK(launch_clamped_glu(ll.moe_gu, ll.moe_y, ct, P, p.ff, p.limit, st));
+        CK(launch_dense_grouped(ct, ll.moe_hs, W, L.e_gateup.data, W, (int64_t) UR * W, ll.moe_gu, UR, ll.moe_start, ll.moe_count, E, P, UR, W, st));
+        CK(activate(P));
         CK(launch_dense_grouped(ct, ll.moe_y, p.ff, L.e_down.data, p.ff, (int64_t) W * p.ff, ll.moe_ds, W, ll.moe_start, ll.moe_count, E, P, W, p.ff, st));
-        return launch_moe_combine(ll.moe_ds, ll.moe_perm, ll.moe_row_of, ll.moe_wt, p.top, W, x, T, st);
+        return launch_moe_combine(ll.moe_ds, ll.moe_perm, ll.moe_row_of, ll.moe_wt, p.top, W, x, T, st, base, xscale);
     }
     CK(cudaMemcpyAsync(ll.moe_count_host, ll.moe_count, (size_t) E * 4, cudaMemcpyDeviceToHost, st));
     CK(cudaMemcpyAsync(ll.moe_count_host + 4096, ll.moe_start, (size_t) E * 4, cudaMemcpyDeviceToHost, st));
@@ -1079,14 +1271,50 @@ static int ff_moe(pb200_model * m, int T, bool prefill, LLayer & L, float * x) {
     const int32_t * cnt = ll.moe_count_host, * start = ll.moe_count_host + 4096;
     for (int e = 0; e < E; e++)
         if (cnt[e] > 0)
-            CK(launch_dense(ct, (const uint8_t *) ll.moe_hs + (size_t) start[e] * W * es, W, (const uint8_t *) L.e_gateup.data + (size_t) e * 2 * p.ff * W * es, W,
-                            ll.moe_gu + (int64_t) start[e] * 2 * p.ff, 2 * p.ff, cnt[e], 2 * p.ff, W, nullptr, nullptr, 0, 1.f, st));
-    CK(launch_clamped_glu(ll.moe_gu, ll.moe_y, ct, P, p.ff, p.limit, st));
+            CK(launch_dense(ct, (const uint8_t *) ll.moe_hs + (size_t) start[e] * W * es, W, (const uint8_t *) L.e_gateup.data + (size_t) e * UR * W * es, W,
+                            ll.moe_gu + (int64_t) start[e] * UR, UR, cnt[e], UR, W, nullptr, nullptr, 0, 1.f, st));
+    CK(activate(P));
     for (int e = 0; e < E; e++)
         if (cnt[e] > 0)
             CK(launch_dense(ct, (const uint8_t *) ll.moe_y + (size_t) start[e] * p.ff * es, p.ff, (const uint8_t *) L.e_down.data + (size_t) e * W * p.ff * es, p.ff,
                             ll.moe_ds + (int64_t) start[e] * W, W, cnt[e], W, p.ff, nullptr, nullptr, 0, 1.f, st));
-    return launch_moe_combine(ll.moe_ds, ll.moe_perm, ll.moe_row_of, ll.moe_wt, p.top, W, x, T, st);
+    return launch_moe_combine(ll.moe_ds, ll.moe_perm, ll.moe_row_of, ll.moe_wt, p.top, W, x, T, st, base, xscale);
+}
+
+// FRAME_POSTNORM: the stream starts as embedding + position vector; x <- x + mult * LN(mixer(x)), x <- x + mult * LN(ff(x)) with weight
+// and bias in LN; the sublayers read x itself (ll.act holds it in the operand type, written by the kernel that updated x).
+static int ll_forward_postnorm(pb200_model * m, const BatchView & b, bool prefill, const int32_t * tokens_dev, const int32_t * want_dev, int nW, int lrow0) {
+    LayerList & ll = *m->ll;
+    cudaStream_t st = m->stream;
+    const int T = b.n_tokens, W = ll.width, ct = ll.ctype;
+    CAT(CAT_ELEM);
+    CK(launch_embed_pos(ll.embed.data, ll.pos_table.data, ct, W, tokens_dev, b, ll.x, ll.act, ct, st));
+    for (size_t ir = 0; ir < ll.runs.size(); ir++) {
+        const LRun & r = ll.runs[ir];
+        LLayer & L = ll.layers[(size_t) r.layer];
+        const bool last = ir + 1 == ll.runs.size();
+        if (L.kind != MIX_ATTENTION) return PB200_ENOTSUP;
+        CK(mix_attention(m, b, prefill, r, L, nullptr, ll.msub));
+        CAT(CAT_NORM);
+        CK(launch_layernorm_affine_residual(ll.msub, L.norm1.data, L.norm1_bias.data, ll.resid_mult, ll.eps, ll.x, (last && L.ff <= 0) ? nullptr : ll.act, ct, T, W, st));
+        if (L.ff > 0) {
+            if (L.ff_kind == FF_MOE) CK(ff_moe(m, T, prefill, L, ll.msub, false));
+            else if (L.ff_kind == FF_RELU2) CK(ff_relu2(m, T, L.gateup, L.down, L.ff, ll.msub));
+            else return PB200_ENOTSUP;
+            CAT(CAT_NORM);
+            CK(launch_layernorm_affine_residual(ll.msub, L.norm2.data, L.norm2_bias.data, ll.resid_mult, ll.eps, ll.x, last ? nullptr : ll.act, ct, T, W, st));
+        }
+        if (ll.tap_on) CK(cudaMemcpyAsync(ll.tap + (int64_t) ir * T * W, ll.x, (size_t) T * W * 4, cudaMemcpyDeviceToDevice, st));
+    }
+    if (nW > 0) {
+        CAT(CAT_HEAD);
+        CK(launch_layernorm_affine(ll.x, want_dev, ll.final_norm.data, ll.final_norm_bias.data, ll.eps, ll.actw, ct, nW, W, st));
+        float * lg = ll.logits + (int64_t) lrow0 * ll.vocab;
+        CK(launch_dense(ct, ll.actw, W, ll.head.data, W, lg, ll.vocab, nW, ll.vocab, W, nullptr, nullptr, 0, ll.logit_scale, st));
+        CK(launch_softcap(lg, (int64_t) nW * ll.vocab, ll.logit_softcap, st));
+    }
+    CAT(-1);
+    return 0;
 }
 
 // FRAME_PRENORM: x <- x + mixer(shift(norm1 x)), x <- x + ff(norm2 x), then the weighted sum over the embedding output and the results
@@ -1115,7 +1343,7 @@ static int ll_forward_prenorm(pb200_model * m, const BatchView & b, bool prefill
         if (L.ff > 0) {
             CAT(CAT_NORM);
             CK(launch_group_rmsnorm(xn, nullptr, L.norm2.data, G, ll.eps, ll.act, ct, T, W, st));
-            if (L.ff_kind == FF_MOE) CK(ff_moe(m, T, prefill, L, xn));
+            if (L.ff_kind == FF_MOE) CK(ff_moe(m, T, prefill, L, xn, true));
             else CK(ff_clamped(m, T, L.gateup, L.down, L.ff, L.ff_limit, xn));
         }
         if (b.max_n == 1 && ir + 1 < ll.runs.size()) {   // one-token entries: the depth average and the next layer's norm + shift in one kernel
@@ -1146,6 +1374,7 @@ static int ll_forward(pb200_model * m, const BatchView & b, bool prefill, const 
     ll.prof_cat.clear();
     CK(tap_prepare(m, b.n_tokens));
     if (ll.frame == FRAME_PRENORM) return ll_forward_prenorm(m, b, prefill, tokens_dev, want_dev, nW, lrow0);
+    if (ll.frame == FRAME_POSTNORM) return ll_forward_postnorm(m, b, prefill, tokens_dev, want_dev, nW, lrow0);
     CAT(CAT_ELEM);
     const int T = b.n_tokens, W = ll.width, ct = ll.ctype;
     CK(launch_embed(ll.embed.data, ct, W, tokens_dev, T, ll.x, ll.x0, st));
@@ -1297,6 +1526,7 @@ int ll_batch_step(pb200_model * m, int n_entries, const pb200_batch_entry * entr
         for (int k = 0; k < e.n_want; k++)
             if (e.want[k] < 0 || e.want[k] >= e.n_tokens) return PB200_EINVAL;
         if (ll.ctx_limited && ll.seq_len[(size_t) e.seq] + e.n_tokens > ll.n_ctx) return PB200_EINVAL;
+        if (ll.max_pos > 0 && ll.seq_len[(size_t) e.seq] + e.n_tokens > ll.max_pos) return PB200_EINVAL;   // no position vector beyond the table
         row_base[(size_t) i] = rows;
         rows += e.n_want;
     }

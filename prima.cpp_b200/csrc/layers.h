@@ -3,7 +3,9 @@
 // Mamba-2 state-space mixer (short causal convolution, selective scan, gated grouped RMS norm); weight-only layer norm with the
 // residual add; tanh-GELU gating; RMS norm in groups, token shift and the depth average of layer results; linear attention with a
 // fixed decay per head; softmax attention over a low-rank latent with a shared rotated key part; the clamped gated feed-forward, dense
-// or as a routed mixture of experts.  Every constant of a mechanism is a parameter, nothing is tied to one model.
+// or as a routed mixture of experts; layer norm with weight and bias on a sublayer's result (post-norm frame), a learned position table,
+// an RMS norm per query / key head, the squared-ReLU feed-forward, the router with sigmoid scores, a choice correction and expert groups,
+// and the tanh soft-cap of the logits.  Every constant of a mechanism is a parameter, nothing is tied to one model.
 // All launchers enqueue on `stream` and return a cudaError_t as int (0 = success).
 #pragma once
 #include <cuda_bf16.h>
@@ -43,9 +45,23 @@ int dense_uses_tensor_cores(int type, int T, int N, int K, int64_t lda, int64_t 
 
 // ---- element-wise / norms; `otype` (T_F32 | T_BF16) is the type of an activation that feeds a dense product ----
 int launch_embed(const void * table, int type, int width, const int32_t * tokens, int n_tokens, float * x, float * x_copy, cudaStream_t stream);
+// x[t] = table[tokens[t]] + pos_table[position of t] (fp32 sum; both tables in `type`); xa (if given) receives x in the operand type
+int launch_embed_pos(const void * table, const void * pos_table, int type, int width, const int32_t * tokens, const BatchView & b, float * x, void * xa,
+                     int otype, cudaStream_t stream);
 int launch_cast(const float * x, void * y, int otype, int64_t n, cudaStream_t stream);
 // y[r] = (x[row] - mean) / sqrt(var + eps) * w, row = rows ? rows[r] : r; var = mean of squared deviations
 int launch_layernorm(const float * x, const int32_t * rows, const float * w, float eps, void * y, int otype, int n_rows, int width, cudaStream_t stream);
+// the same with a bias: y[r] = (x[row] - mean) / sqrt(var + eps) * w + bias   (bias may be null)
+int launch_layernorm_affine(const float * x, const int32_t * rows, const float * w, const float * bias, float eps, void * y, int otype, int n_rows, int width,
+                            cudaStream_t stream);
+// x[t] += mult * (layernorm(m[t]) * w + bias), then xa[t] = x[t] in the operand type (xa may be null): the norm on a sublayer's result, the
+// residual sum (fp32) and the next sublayer's operand in one pass
+int launch_layernorm_affine_residual(const float * m, const float * w, const float * bias, float mult, float eps, float * x, void * xa, int otype, int n_rows,
+                                     int width, cudaStream_t stream);
+// y[i] = max(u[i], 0)^2 -> operand type
+int launch_relu2(const float * u, void * y, int otype, int64_t n, cudaStream_t stream);
+// x[i] <- cap * tanh(x[i] / cap), in place
+int launch_softcap(float * x, int64_t n, float cap, cudaStream_t stream);
 // x[t] += layernorm(m[t]) * w      (the post-norm of a sublayer and the residual sum, fp32)
 int launch_layernorm_residual(const float * m, const float * w, float eps, float * x, int n_rows, int width, cudaStream_t stream);
 // both at once: x[t] += layernorm(m[t]) * wa, then y[t] = layernorm(x[t]) * wb (the next sublayer's input)
@@ -65,6 +81,7 @@ struct AttnParams {
     int keep_first = 0;       // ... or j < keep_first
     int cache_rows = 0;       // rows per slot: positions < keep_first at their own row, later ones in a ring over the rest
     int shared_dim = 0;       // prompt kernels: the last shared_dim of a key's dim entries come from one array all heads share
+    int gated = 1;            // the fused projection ends with one gate logit per head (0: q | k | v only, the output is not gated)
 };
 // Where the attention kernels read their inputs (fp32 rows, strides in floats).  Prompt kernels read keys and values of the batch:
 // k rows hold [kv_heads][dim - shared_dim], ks rows [shared_dim]; v rows [kv_heads][vdim].  Decode kernels read q and gate here and
@@ -78,7 +95,7 @@ struct AttnIO {
     int gate_mode = 0;                                  // 0: no gate, 1: one logit per head, 2: one per output element [heads][vdim]
     int64_t k_row = 0, v_row = 0;
 };
-__host__ __device__ inline int attn_qkvg_cols(const AttnParams & a) { return a.heads * a.dim + a.kv_heads * a.dim + a.kv_heads * a.vdim + a.heads; }
+__host__ __device__ inline int attn_qkvg_cols(const AttnParams & a) { return a.heads * a.dim + a.kv_heads * a.dim + a.kv_heads * a.vdim + (a.gated ? a.heads : 0); }
 // rows of a slot's cache so that every position a later token may still see is present, capped at n_ctx
 inline int attn_cache_rows(int window, int keep_first, int n_ctx) {
     if (window <= 0) return n_ctx;
@@ -89,6 +106,10 @@ inline int attn_cache_rows(int window, int keep_first, int n_ctx) {
 // kcache / vcache: base of the layer run's cache, slot s at + s * slot_stride floats; rows of kv_heads*dim / kv_heads*vdim floats.
 int launch_attn_kv_store(const float * qkvg, const BatchView & b, const AttnParams & a, float * kcache, float * vcache, int64_t slot_stride,
                          cudaStream_t stream);
+// the same after an RMS norm of every query head (weight wq [dim]) and key head (wk [dim]) of the fused projection, in place:
+// v <- v / sqrt(mean(v^2) + eps) * w per head; the cache receives the normed keys
+int launch_attn_qknorm_kv_store(float * qkvg, const BatchView & b, const AttnParams & a, const float * wq, const float * wk, float eps, float * kcache,
+                                float * vcache, int64_t slot_stride, cudaStream_t stream);
 // entries that start at position 0: keys and values are read from the batch itself
 int launch_attn_window_prefill(const float * qkvg, const BatchView & b, const AttnParams & a, void * out, int otype, cudaStream_t stream);
 // one-token entries: keys and values come from the cache (the token's own row already stored)
@@ -190,23 +211,35 @@ int launch_clamped_glu(const float * gu, void * y, int otype, int n_tokens, int 
 struct MoeParams {
     int experts = 0, top = 0, ff = 0;
     float limit = 0.f;
+    int act = 0;              // expert form: 0 = clamped gated unit (rows gate | up, 2 ff per expert), 1 = max(up, 0)^2 (rows up, ff per expert)
+    int groups = 1, keep_groups = 1;   // launch_moe_route_sigmoid: equal groups of neighbouring experts, of which the best keep_groups stay eligible
+    float route_scale = 1.f;           // launch_moe_route_sigmoid: factor on the normalised weights
 };
+__host__ __device__ inline int moe_up_rows(const MoeParams & p) { return p.act == 0 ? 2 * p.ff : p.ff; }
 // z = h W_r^T + bias in fp32 (h: the operand-type activations); idx[t][0..top) the experts with the largest z (ties: lower index),
 // wt[t][..] the softmax over the chosen logits
 int launch_moe_route(const void * h, int htype, const float * wr, const float * bias, const MoeParams & p, int width, int32_t * idx, float * wt,
                      int n_tokens, cudaStream_t stream);
-// few tokens: every (token, chosen expert) streams its expert's rows.  y[t][k][ff] = clamped_glu(expert idx[t][k] of gateup) -> operand type
+// s = sigmoid(h W_r^T) in fp32; choice score c = s + correction; score of a group = its two largest c summed (its only one in a group of
+// one); experts outside the keep_groups best groups are not eligible; idx[t][0..top) the eligible experts with the largest c (ties: lower
+// index), wt[t][k] = s[idx] / (sum of the chosen s + 1e-20) * route_scale.  shared_gate (may be null, then sg_out is not written):
+// sg_out[t] = sigmoid(h . shared_gate), the factor on a shared expert's result.
+int launch_moe_route_sigmoid(const void * h, int htype, const float * wr, const float * correction, const MoeParams & p, int width, const float * shared_gate,
+                             int32_t * idx, float * wt, float * sg_out, int n_tokens, cudaStream_t stream);
+// few tokens: every (token, chosen expert) streams its expert's rows.  y[t][k][ff] = act(expert idx[t][k] of gateup) -> operand type
 int launch_moe_gateup_rows(const void * h, int type, const void * gateup, const int32_t * idx, const MoeParams & p, int width, void * y, int n_tokens,
                            cudaStream_t stream);
-// x[t] += sum_k wt[t][k] * down[idx[t][k]] y[t][k]      (k in the order of the choice)
+// x[t] = base(x[t]) + sum_k wt[t][k] * down[idx[t][k]] y[t][k]      (k in the order of the choice)
+// base: MOE_ADD x[t] itself, MOE_SET zero, MOE_SCALE x[t] * xscale[t] (a gated shared expert's result waits in x)
+enum : int { MOE_ADD = 0, MOE_SET = 1, MOE_SCALE = 2 };
 int launch_moe_down_rows(const void * y, int type, const void * down, const int32_t * idx, const float * wt, const MoeParams & p, int width, float * x,
-                         int n_tokens, cudaStream_t stream);
+                         int n_tokens, cudaStream_t stream, int base = MOE_ADD, const float * xscale = nullptr);
 // many tokens: pairs (t, k) sorted by expert (stable).  count[e], start[e] (exclusive prefix), perm[r] = pair index t * top + k of sorted row r
 int launch_moe_sort(const int32_t * idx, const MoeParams & p, int n_tokens, int32_t * count, int32_t * start, int32_t * perm, cudaStream_t stream);
 // hs[r] = h[perm[r] / top]   (rows of `width` operand-type elements)
 int launch_moe_gather(const void * h, int type, const int32_t * perm, int top, int width, void * hs, int n_rows, cudaStream_t stream);
-// x[t] += sum_k wt[t][k] * ds[row_of[t * top + k]],  row_of = inverse of perm (computed by the kernel from perm)
+// x[t] = base(x[t]) + sum_k wt[t][k] * ds[row_of[t * top + k]],  row_of = inverse of perm (computed by the kernel from perm)
 int launch_moe_combine(const float * ds, const int32_t * perm, int32_t * row_of, const float * wt, int top, int width, float * x, int n_tokens,
-                       cudaStream_t stream);
+                       cudaStream_t stream, int base = MOE_ADD, const float * xscale = nullptr);
 
 }  // namespace pb

@@ -34,10 +34,10 @@ __global__ void k_cast(const float * __restrict__ x, OT * __restrict__ y, int64_
     if (i < n) put(y, i, x[i]);
 }
 
-// layer norm with a weight and no bias; two passes over the row (mean, then the mean of squared deviations)
+// layer norm with a weight and an optional bias; two passes over the row (mean, then the mean of squared deviations)
 template <typename OT, bool RESID>
-__global__ void __launch_bounds__(256) k_layernorm(const float * __restrict__ x, const int32_t * __restrict__ rows, const float * __restrict__ w, float eps,
-                                                   OT * __restrict__ y, float * __restrict__ xres, int width) {
+__global__ void __launch_bounds__(256) k_layernorm(const float * __restrict__ x, const int32_t * __restrict__ rows, const float * __restrict__ w,
+                                                   const float * __restrict__ bias, float eps, OT * __restrict__ y, float * __restrict__ xres, int width) {
     __shared__ float red[33];
     const int r = blockIdx.x;
     const float * in = x + (int64_t) (rows ? rows[r] : r) * width;
@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(256) k_layernorm(const float * __restrict__ x,
     const float var = block_sum(q, red) / (float) width;
     const float inv = 1.f / sqrtf(var + eps);
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float v = (in[i] - mean) * inv * w[i];
+        const float v = (in[i] - mean) * inv * w[i] + (bias ? bias[i] : 0.f);
         if constexpr (RESID) xres[(int64_t) r * width + i] += v;
         else put(y, (int64_t) r * width + i, v);
     }
@@ -81,6 +81,57 @@ __global__ void __launch_bounds__(256) k_layernorm_residual_next(const float * _
     for (int i = threadIdx.x; i < width; i += blockDim.x) { const float d = xr[i] - mean2; q2 = fmaf(d, d, q2); }
     const float inv2 = 1.f / sqrtf(block_sum(q2, red) / (float) width + eps);
     for (int i = threadIdx.x; i < width; i += blockDim.x) put(y, (int64_t) r * width + i, (xr[i] - mean2) * inv2 * wb[i]);
+}
+
+// x[t] += mult * (layernorm(m[t]) * w + bias); xa[t] = x[t] in the operand type.  The row of m is kept in registers (width <= 256 * LNR)
+// or re-read; x is read and written once.
+template <typename OT>
+__global__ void __launch_bounds__(256) k_layernorm_affine_residual(const float * __restrict__ m, const float * __restrict__ w, const float * __restrict__ bias,
+                                                                   float mult, float eps, float * __restrict__ x, OT * __restrict__ xa, int width) {
+    __shared__ float red[33];
+    const int r = blockIdx.x;
+    const float * in = m + (int64_t) r * width;
+    float * xr = x + (int64_t) r * width;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) s += in[i];
+    const float mean = block_sum(s, red) / (float) width;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) { const float d = in[i] - mean; q = fmaf(d, d, q); }
+    const float inv = 1.f / sqrtf(block_sum(q, red) / (float) width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = xr[i] + mult * ((in[i] - mean) * inv * w[i] + (bias ? bias[i] : 0.f));
+        xr[i] = v;
+        if (xa) put(xa, (int64_t) r * width + i, v);
+    }
+}
+
+template <typename OT>
+__global__ void k_relu2(const float * __restrict__ u, OT * __restrict__ y, int64_t n) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = fmaxf(u[i], 0.f);
+    put(y, i, v * v);
+}
+__global__ void k_softcap(float * __restrict__ x, int64_t n, float cap) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+
+// x[t] = table[token] + pos_table[position]; positions count from the entry's pos0
+template <typename WT, typename OT>
+__global__ void k_embed_pos(const WT * __restrict__ table, const WT * __restrict__ ptab, int width, const int32_t * __restrict__ tokens,
+                            const int32_t * __restrict__ off, const int32_t * __restrict__ pos0, const int32_t * __restrict__ entry_of, float * __restrict__ x,
+                            OT * __restrict__ xa) {
+    const int t = blockIdx.x;
+    const int e = entry_of[t];
+    const int64_t p = pos0[e] + (t - off[e]);
+    const WT * row = table + (int64_t) tokens[t] * width;
+    const WT * prow = ptab + p * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = ld_f(row, i) + ld_f(prow, i);
+        x[(int64_t) t * width + i] = v;
+        if (xa) put(xa, (int64_t) t * width + i, v);
+    }
 }
 
 template <typename OT>
@@ -149,6 +200,38 @@ __global__ void k_attn_kv_store(const float * __restrict__ qkvg, const int32_t *
     const float * src = qkvg + (int64_t) t * C + a.heads * a.dim;
     float * kd = kcache + (int64_t) slot[e] * slot_stride + (int64_t) row * KD;
     float * vd = vcache + (int64_t) slot[e] * slot_stride + (int64_t) row * VD;
+    for (int i = threadIdx.x; i < KD; i += blockDim.x) kd[i] = src[i];
+    for (int i = threadIdx.x; i < VD; i += blockDim.x) vd[i] = src[KD + i];
+}
+
+// One CTA per token.  First every query head and key head of the token's fused projection is divided by its root mean square and
+// multiplied by the weight all heads share (one warp per head, in place); then the rows later tokens can still see go to the cache.
+__global__ void __launch_bounds__(256) k_attn_qknorm_kv_store(float * __restrict__ qkvg, const int32_t * __restrict__ slot, const int32_t * __restrict__ off,
+                                                              const int32_t * __restrict__ pos0, const int32_t * __restrict__ entry_of, AttnParams a,
+                                                              const float * __restrict__ wq, const float * __restrict__ wk, float eps,
+                                                              float * __restrict__ kcache, float * __restrict__ vcache, int64_t slot_stride) {
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int KD = a.kv_heads * a.dim, VD = a.kv_heads * a.vdim, C = attn_qkvg_cols(a);
+    float * row = qkvg + (int64_t) t * C;
+    for (int hh = warp; hh < a.heads + a.kv_heads; hh += nw) {
+        float * v = row + (int64_t) hh * a.dim;                   // q heads, then k heads, back to back
+        const float * w = hh < a.heads ? wq : wk;
+        float ss = 0.f;
+        for (int i = lane; i < a.dim; i += 32) ss = fmaf(v[i], v[i], ss);
+        const float inv = 1.f / sqrtf(wsum(ss) / (float) a.dim + eps);
+        for (int i = lane; i < a.dim; i += 32) v[i] = v[i] * inv * w[i];
+    }
+    __syncthreads();
+    const int e = entry_of[t];
+    const int n = off[e + 1] - off[e];
+    const int p = pos0[e] + (t - off[e]), pend = pos0[e] + n;
+    const int keep = min(a.keep_first, a.cache_rows), ring = a.cache_rows - keep;
+    if (p >= keep && (ring <= 0 || p < pend - ring)) return;
+    const int crow = cache_row(p, keep, max(ring, 1));
+    const float * src = row + a.heads * a.dim;
+    float * kd = kcache + (int64_t) slot[e] * slot_stride + (int64_t) crow * KD;
+    float * vd = vcache + (int64_t) slot[e] * slot_stride + (int64_t) crow * VD;
     for (int i = threadIdx.x; i < KD; i += blockDim.x) kd[i] = src[i];
     for (int i = threadIdx.x; i < VD; i += blockDim.x) vd[i] = src[KD + i];
 }
@@ -701,13 +784,54 @@ int launch_cast(const float * x, void * y, int otype, int64_t n, cudaStream_t st
 int launch_layernorm(const float * x, const int32_t * rows, const float * w, float eps, void * y, int otype, int n_rows, int width, cudaStream_t st) {
     if (n_rows <= 0) return 0;
     return ck_launch([&] {
-        if (otype == T_BF16) k_layernorm<__nv_bfloat16, false><<<n_rows, 256, 0, st>>>(x, rows, w, eps, (__nv_bfloat16 *) y, nullptr, width);
-        else k_layernorm<float, false><<<n_rows, 256, 0, st>>>(x, rows, w, eps, (float *) y, nullptr, width);
+        if (otype == T_BF16) k_layernorm<__nv_bfloat16, false><<<n_rows, 256, 0, st>>>(x, rows, w, nullptr, eps, (__nv_bfloat16 *) y, nullptr, width);
+        else k_layernorm<float, false><<<n_rows, 256, 0, st>>>(x, rows, w, nullptr, eps, (float *) y, nullptr, width);
+    });
+}
+int launch_layernorm_affine(const float * x, const int32_t * rows, const float * w, const float * bias, float eps, void * y, int otype, int n_rows, int width,
+                            cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    return ck_launch([&] {
+        if (otype == T_BF16) k_layernorm<__nv_bfloat16, false><<<n_rows, 256, 0, st>>>(x, rows, w, bias, eps, (__nv_bfloat16 *) y, nullptr, width);
+        else k_layernorm<float, false><<<n_rows, 256, 0, st>>>(x, rows, w, bias, eps, (float *) y, nullptr, width);
+    });
+}
+int launch_layernorm_affine_residual(const float * m, const float * w, const float * bias, float mult, float eps, float * x, void * xa, int otype, int n_rows,
+                                     int width, cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    return ck_launch([&] {
+        if (otype == T_BF16) k_layernorm_affine_residual<__nv_bfloat16><<<n_rows, 256, 0, st>>>(m, w, bias, mult, eps, x, (__nv_bfloat16 *) xa, width);
+        else k_layernorm_affine_residual<float><<<n_rows, 256, 0, st>>>(m, w, bias, mult, eps, x, (float *) xa, width);
+    });
+}
+int launch_relu2(const float * u, void * y, int otype, int64_t n, cudaStream_t st) {
+    if (n <= 0) return 0;
+    const unsigned grid = (unsigned) ((n + 255) / 256);
+    return ck_launch([&] {
+        if (otype == T_BF16) k_relu2<__nv_bfloat16><<<grid, 256, 0, st>>>(u, (__nv_bfloat16 *) y, n);
+        else k_relu2<float><<<grid, 256, 0, st>>>(u, (float *) y, n);
+    });
+}
+int launch_softcap(float * x, int64_t n, float cap, cudaStream_t st) {
+    if (n <= 0 || !(cap > 0.f)) return 0;
+    return ck_launch([&] { k_softcap<<<(unsigned) ((n + 255) / 256), 256, 0, st>>>(x, n, cap); });
+}
+int launch_embed_pos(const void * table, const void * pos_table, int type, int width, const int32_t * tokens, const BatchView & b, float * x, void * xa,
+                     int otype, cudaStream_t st) {
+    if (b.n_tokens <= 0) return 0;
+    if ((xa && otype != type) || !pos_table) return (int) cudaErrorInvalidValue;
+    return ck_launch([&] {
+        if (type == T_BF16)
+            k_embed_pos<__nv_bfloat16, __nv_bfloat16><<<b.n_tokens, 128, 0, st>>>((const __nv_bfloat16 *) table, (const __nv_bfloat16 *) pos_table, width, tokens,
+                                                                                   b.off, b.pos0, b.entry_of, x, (__nv_bfloat16 *) xa);
+        else
+            k_embed_pos<float, float><<<b.n_tokens, 128, 0, st>>>((const float *) table, (const float *) pos_table, width, tokens, b.off, b.pos0, b.entry_of, x,
+                                                                   (float *) xa);
     });
 }
 int launch_layernorm_residual(const float * m, const float * w, float eps, float * x, int n_rows, int width, cudaStream_t st) {
     if (n_rows <= 0) return 0;
-    return ck_launch([&] { k_layernorm<float, true><<<n_rows, 256, 0, st>>>(m, nullptr, w, eps, nullptr, x, width); });
+    return ck_launch([&] { k_layernorm<float, true><<<n_rows, 256, 0, st>>>(m, nullptr, w, nullptr, eps, nullptr, x, width); });
 }
 int launch_layernorm_residual_next(const float * m, const float * wa, const float * wb, float eps, float * x, void * y, int otype, int n_rows, int width,
                                    cudaStream_t st) {
@@ -734,6 +858,15 @@ int launch_argmax_rows(const float * logits, int n, int n_rows, int32_t * out, c
 int launch_attn_kv_store(const float * qkvg, const BatchView & b, const AttnParams & a, float * kcache, float * vcache, int64_t slot_stride, cudaStream_t st) {
     if (b.n_tokens <= 0) return 0;
     return ck_launch([&] { k_attn_kv_store<<<b.n_tokens, 128, 0, st>>>(qkvg, b.slot, b.off, b.pos0, b.entry_of, a, kcache, vcache, slot_stride); });
+}
+
+int launch_attn_qknorm_kv_store(float * qkvg, const BatchView & b, const AttnParams & a, const float * wq, const float * wk, float eps, float * kcache,
+                                float * vcache, int64_t slot_stride, cudaStream_t st) {
+    if (b.n_tokens <= 0) return 0;
+    if (!wq || !wk) return (int) cudaErrorInvalidValue;
+    return ck_launch([&] {
+        k_attn_qknorm_kv_store<<<b.n_tokens, 256, 0, st>>>(qkvg, b.slot, b.off, b.pos0, b.entry_of, a, wq, wk, eps, kcache, vcache, slot_stride);
+    });
 }
 
 #define PB_NV_DISPATCH(NVV, CALL)                                  \
@@ -815,7 +948,7 @@ static AttnIO attn_io_fused(const float * qkvg, const AttnParams & a) {
     io.q = qkvg; io.ldq = C;
     io.k = qkvg + (int64_t) a.heads * a.dim; io.ldk = C;
     io.v = io.k + (int64_t) a.kv_heads * a.dim; io.ldv = C;
-    io.gate = io.v + (int64_t) a.kv_heads * a.vdim; io.ldg = C; io.gate_mode = 1;
+    io.gate = io.v + (int64_t) a.kv_heads * a.vdim; io.ldg = C; io.gate_mode = a.gated ? 1 : 0;
     io.k_row = (int64_t) a.kv_heads * a.dim; io.v_row = (int64_t) a.kv_heads * a.vdim;
     return io;
 }

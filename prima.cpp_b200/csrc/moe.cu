@@ -1,5 +1,8 @@
-// prima.cpp_b200/csrc/moe.cu — routed mixture of clamped gated experts (declarations and semantics: layers.h).  The router runs in fp32:
-// logits, the choice of the `top` largest (ties: the lower index) and the softmax over the chosen logits.  Two ways through the experts:
+// prima.cpp_b200/csrc/moe.cu — routed mixture of experts (declarations and semantics: layers.h).  An expert is a clamped gated unit or a
+// squared-ReLU unit (MoeParams::act).  The router runs in fp32, in one of two forms: logits + bias, the `top` largest (ties: the lower
+// index), softmax over the chosen logits (k_moe_route); or sigmoid scores, a per-expert correction added for the choice only, the choice
+// limited to the best groups of neighbouring experts, weights = the uncorrected scores of the chosen divided by their sum, times a factor
+// (k_moe_route_sigmoid, which also yields the sigmoid gate of a shared expert).  Two ways through the experts:
 //   few tokens   every (token, chosen expert) pair streams the rows of its expert (weights are read once per pair, mostly from L2 when
 //                tokens share experts); no host round trip, so a decode step stays one replayable graph
 //   many tokens  pairs are sorted by expert (stable counting sort on the device), activations gathered into expert-contiguous rows, the
@@ -88,6 +91,86 @@ __global__ void __launch_bounds__(256) k_moe_route(const HT * __restrict__ h, co
     if (lane < p.top) wt[(int64_t) t * p.top + lane] = pe / sum;
 }
 
+// warp arg-max over v[0..n) in shared memory (ties: the lower index); every lane gets (value, index); index 0x7fffffff if nothing is finite
+__device__ __forceinline__ void warp_argmax(const float * v, int n, int lane, float & best, int & bi) {
+    best = -INFINITY;
+    bi = 0x7fffffff;
+    for (int e = lane; e < n; e += 32) {
+        const float c = v[e];
+        if (c > best) { best = c; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+}
+
+// one CTA per token: sigmoid scores, choice with the correction among the experts of the best groups, weights from the plain scores
+template <typename HT>
+__global__ void __launch_bounds__(256) k_moe_route_sigmoid(const HT * __restrict__ h, const float * __restrict__ wr, const float * __restrict__ corr, MoeParams p,
+                                                           int width, const float * __restrict__ sgw, int32_t * __restrict__ idx, float * __restrict__ wt,
+                                                           float * __restrict__ sg_out) {
+    extern __shared__ float sm[];
+    float * hs = sm;                 // [width]
+    float * sc = hs + width;         // [experts] sigmoid scores
+    float * ch = sc + p.experts;     // [experts] choice scores, -inf once taken or not eligible
+    float * gs = ch + p.experts;     // [groups] group scores
+    float * kp = gs + p.groups;      // [groups] 1: the group stays eligible
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) hs[i] = ld_f(h, (int64_t) t * width + i);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int e = warp; e < p.experts + (sgw ? 1 : 0); e += nw) {
+        if (e == p.experts) {        // the shared expert's gate rides along as one more row
+            const float acc = wsum(dot_lane8(sgw, hs, width, lane));
+            if (lane == 0) sg_out[t] = sigmoid_f(acc);
+        } else {
+            const float acc = wsum(dot_lane8(wr + (int64_t) e * width, hs, width, lane));
+            if (lane == 0) { const float s = sigmoid_f(acc); sc[e] = s; ch[e] = s + corr[e]; }
+        }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    const int per = p.experts / p.groups;
+    if (p.groups > 1 && p.keep_groups < p.groups) {
+        for (int g = lane; g < p.groups; g += 32) {   // the two largest choice scores of the group, summed
+            float a = -INFINITY, b = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; e++) {
+                const float c = ch[e];
+                if (c > a) { b = a; a = c; } else if (c > b) b = c;
+            }
+            gs[g] = per > 1 ? a + b : a;
+            kp[g] = 0.f;
+        }
+        __syncwarp();
+        // the keep_groups best groups stay (ties: the lower index); the others lose their experts
+        for (int k = 0; k < p.keep_groups; k++) {
+            float best; int bi;
+            warp_argmax(gs, p.groups, lane, best, bi);
+            if (bi == 0x7fffffff) break;
+            if (lane == 0) { gs[bi] = -INFINITY; kp[bi] = 1.f; }
+            __syncwarp();
+        }
+        for (int g = 0; g < p.groups; g++)
+            if (kp[g] == 0.f)
+                for (int e = g * per + lane; e < (g + 1) * per; e += 32) ch[e] = -INFINITY;
+        __syncwarp();
+    }
+    float mine = 0.f;   // lane k keeps the score of the k-th chosen expert (top <= 32)
+    for (int k = 0; k < p.top; k++) {
+        float best; int bi;
+        warp_argmax(ch, p.experts, lane, best, bi);
+        if (bi == 0x7fffffff) bi = 0;             // only with non-finite scores
+        if (lane == k) mine = sc[bi];
+        if (lane == 0) { idx[(int64_t) t * p.top + k] = bi; ch[bi] = -INFINITY; }
+        __syncwarp();
+    }
+    const float sum = wsum(lane < p.top ? mine : 0.f);
+    if (lane < p.top) wt[(int64_t) t * p.top + lane] = mine / (sum + 1e-20f) * p.route_scale;
+}
+
 // grid (ceil(ff / 8), pairs): warp -> row j of gate and of up of the pair's expert
 template <typename WT, bool VEC>
 __global__ void __launch_bounds__(256) k_moe_gateup_rows(const WT * __restrict__ h, const WT * __restrict__ gateup, const int32_t * __restrict__ idx, MoeParams p,
@@ -96,9 +179,14 @@ __global__ void __launch_bounds__(256) k_moe_gateup_rows(const WT * __restrict__
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int j = blockIdx.x * 8 + warp;
     if (j >= p.ff) return;
-    const WT * we = gateup + (int64_t) idx[pair] * 2 * p.ff * width;
+    const WT * we = gateup + (int64_t) idx[pair] * moe_up_rows(p) * width;
     const WT * a = h + (int64_t) t * width;
     float g = dot_part<WT, VEC>(we + (int64_t) j * width, a, width, lane);
+    if (p.act == 1) {   // squared ReLU of the only row
+        g = fmaxf(wsum(g), 0.f);
+        if (lane == 0) put(y, (int64_t) pair * p.ff + j, g * g);
+        return;
+    }
     float u = dot_part<WT, VEC>(we + (int64_t) (p.ff + j) * width, a, width, lane);
     g = wsum(g);
     u = wsum(u);
@@ -111,7 +199,8 @@ __global__ void __launch_bounds__(256) k_moe_gateup_rows(const WT * __restrict__
 // grid (ceil(width / 8), tokens): warp -> output n of the token, summed over its experts in the order of the choice
 template <typename WT, bool VEC>
 __global__ void __launch_bounds__(256) k_moe_down_rows(const WT * __restrict__ y, const WT * __restrict__ down, const int32_t * __restrict__ idx,
-                                                       const float * __restrict__ wt, MoeParams p, int width, float * __restrict__ x) {
+                                                       const float * __restrict__ wt, MoeParams p, int width, float * __restrict__ x, int base,
+                                                       const float * __restrict__ xscale) {
     const int t = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x * 8 + warp;
@@ -123,7 +212,10 @@ __global__ void __launch_bounds__(256) k_moe_down_rows(const WT * __restrict__ y
         const float d = wsum(dot_part<WT, VEC>(w, y + (int64_t) pair * p.ff, p.ff, lane));
         acc = fmaf(wt[pair], d, acc);
     }
-    if (lane == 0) x[(int64_t) t * width + n] += acc;
+    if (lane == 0) {
+        float * xo = x + (int64_t) t * width + n;
+        *xo = (base == MOE_SET ? 0.f : base == MOE_SCALE ? *xo * xscale[t] : *xo) + acc;
+    }
 }
 
 // ---- sort by expert ----
@@ -173,12 +265,13 @@ __global__ void k_moe_invert(const int32_t * __restrict__ perm, int32_t * __rest
     if (r < n_pairs) row_of[perm[r]] = r;
 }
 __global__ void k_moe_combine(const float * __restrict__ ds, const int32_t * __restrict__ row_of, const float * __restrict__ wt, int top, int width,
-                              float * __restrict__ x) {
+                              float * __restrict__ x, int base, const float * __restrict__ xscale) {
     const int t = blockIdx.x;
     for (int n = threadIdx.x; n < width; n += blockDim.x) {
         float acc = 0.f;
         for (int k = 0; k < top; k++) acc = fmaf(wt[(int64_t) t * top + k], ds[(int64_t) row_of[(int64_t) t * top + k] * width + n], acc);
-        x[(int64_t) t * width + n] += acc;
+        float * xo = x + (int64_t) t * width + n;
+        *xo = (base == MOE_SET ? 0.f : base == MOE_SCALE ? *xo * xscale[t] : *xo) + acc;
     }
 }
 
@@ -204,6 +297,24 @@ int launch_moe_route(const void * h, int htype, const float * wr, const float * 
     if (rc) return rc;
     return ck_launch([&] { k_moe_route<float><<<n_tokens, 256, smem, st>>>((const float *) h, wr, bias, p, width, idx, wt); });
 }
+int launch_moe_route_sigmoid(const void * h, int htype, const float * wr, const float * correction, const MoeParams & p, int width, const float * shared_gate,
+                             int32_t * idx, float * wt, float * sg_out, int n_tokens, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (!moe_ok(p) || p.groups <= 0 || p.experts % p.groups || p.keep_groups <= 0 || p.keep_groups > p.groups || (shared_gate && !sg_out) ||
+        (int64_t) p.keep_groups * (p.experts / p.groups) < p.top)
+        return (int) cudaErrorInvalidValue;
+    const size_t smem = ((size_t) width + 2 * (size_t) p.experts + 2 * (size_t) p.groups) * sizeof(float);
+    if (htype == T_BF16) {
+        int rc = raise_smem(k_moe_route_sigmoid<__nv_bfloat16>, smem);
+        if (rc) return rc;
+        return ck_launch([&] {
+            k_moe_route_sigmoid<__nv_bfloat16><<<n_tokens, 256, smem, st>>>((const __nv_bfloat16 *) h, wr, correction, p, width, shared_gate, idx, wt, sg_out);
+        });
+    }
+    int rc = raise_smem(k_moe_route_sigmoid<float>, smem);
+    if (rc) return rc;
+    return ck_launch([&] { k_moe_route_sigmoid<float><<<n_tokens, 256, smem, st>>>((const float *) h, wr, correction, p, width, shared_gate, idx, wt, sg_out); });
+}
 int launch_moe_gateup_rows(const void * h, int type, const void * gateup, const int32_t * idx, const MoeParams & p, int width, void * y, int n_tokens,
                            cudaStream_t st) {
     if (n_tokens <= 0) return 0;
@@ -221,18 +332,18 @@ int launch_moe_gateup_rows(const void * h, int type, const void * gateup, const 
     });
 }
 int launch_moe_down_rows(const void * y, int type, const void * down, const int32_t * idx, const float * wt, const MoeParams & p, int width, float * x,
-                         int n_tokens, cudaStream_t st) {
+                         int n_tokens, cudaStream_t st, int base, const float * xscale) {
     if (n_tokens <= 0) return 0;
-    if (!moe_ok(p)) return (int) cudaErrorInvalidValue;
+    if (!moe_ok(p) || (base == MOE_SCALE && !xscale)) return (int) cudaErrorInvalidValue;
     const dim3 grid((unsigned) ((width + 7) / 8), (unsigned) n_tokens);
     return ck_launch([&] {
         if (type == T_BF16) {
             using B = __nv_bfloat16;
-            if (vec_ok<B>(y, down, p.ff)) k_moe_down_rows<B, true><<<grid, 256, 0, st>>>((const B *) y, (const B *) down, idx, wt, p, width, x);
-            else k_moe_down_rows<B, false><<<grid, 256, 0, st>>>((const B *) y, (const B *) down, idx, wt, p, width, x);
+            if (vec_ok<B>(y, down, p.ff)) k_moe_down_rows<B, true><<<grid, 256, 0, st>>>((const B *) y, (const B *) down, idx, wt, p, width, x, base, xscale);
+            else k_moe_down_rows<B, false><<<grid, 256, 0, st>>>((const B *) y, (const B *) down, idx, wt, p, width, x, base, xscale);
         } else {
-            if (vec_ok<float>(y, down, p.ff)) k_moe_down_rows<float, true><<<grid, 256, 0, st>>>((const float *) y, (const float *) down, idx, wt, p, width, x);
-            else k_moe_down_rows<float, false><<<grid, 256, 0, st>>>((const float *) y, (const float *) down, idx, wt, p, width, x);
+            if (vec_ok<float>(y, down, p.ff)) k_moe_down_rows<float, true><<<grid, 256, 0, st>>>((const float *) y, (const float *) down, idx, wt, p, width, x, base, xscale);
+            else k_moe_down_rows<float, false><<<grid, 256, 0, st>>>((const float *) y, (const float *) down, idx, wt, p, width, x, base, xscale);
         }
     });
 }
@@ -252,12 +363,13 @@ int launch_moe_gather(const void * h, int type, const int32_t * perm, int top, i
     });
 }
 int launch_moe_combine(const float * ds, const int32_t * perm, int32_t * row_of, const float * wt, int top, int width, float * x, int n_tokens,
-                       cudaStream_t st) {
+                       cudaStream_t st, int base, const float * xscale) {
     if (n_tokens <= 0) return 0;
+    if (base == MOE_SCALE && !xscale) return (int) cudaErrorInvalidValue;
     const int n_pairs = n_tokens * top;
     int rc = ck_launch([&] { k_moe_invert<<<(unsigned) ((n_pairs + 255) / 256), 256, 0, st>>>(perm, row_of, n_pairs); });
     if (rc) return rc;
-    return ck_launch([&] { k_moe_combine<<<n_tokens, 256, 0, st>>>(ds, row_of, wt, top, width, x); });
+    return ck_launch([&] { k_moe_combine<<<n_tokens, 256, 0, st>>>(ds, row_of, wt, top, width, x, base, xscale); });
 }
 
 }  // namespace pb
