@@ -1,6 +1,7 @@
 """Throughput of the layer-list family at sizes that resemble a real model's layers, random weights, beside the closest existing model at
 equal width / feed-forward / head sizes / number of layer runs: Vamidra beside the Llama graph over Q4_K weights (``bench.py --arch
-vamidra``), Mumizen beside Vamidra (``bench.py --arch mumizen``, :func:`run_mumizen`).  Prints one JSON line.
+vamidra``), Mumizen beside Vamidra (``bench.py --arch mumizen``, :func:`run_mumizen`), Sapudra beside Vamidra and, for its experts, Mumizen
+(``bench.py --arch sapudra``, :func:`run_sapudra`).  Prints one JSON line.
 
 Per size: prompt tokens/s (one sequence of 512 and 2048 tokens) and decode tokens/s (batch 1 and 8 at a 1024-token context) of both
 models through their public entry points (host token ids in, host logits / greedy tokens out), the device time of a prompt and of a
@@ -63,6 +64,8 @@ def peaks():
 def run(args, pkg, lib):
     if args.arch == "mumizen":
         return run_mumizen(args, pkg, lib)
+    if args.arch == "sapudra":
+        return run_sapudra(args, pkg, lib)
     import numpy as np
     import torch
     hbm, tflops, src = peaks()
@@ -297,6 +300,50 @@ def mumizen_products(cfg, prompt):
     return out, expert
 
 
+def measure(m, vocab, args, rng, CTX=1024):
+    """Whole-model prompt (512 / 2048 tokens) and decode (batch 1 / 8 at a CTX-token context) throughput through the public entry points, with the
+    device time of one prompt and one step by kernel category."""
+    v = {}
+    for T in (512, 2048):
+        toks = rng.integers(0, vocab, T).tolist()
+
+        def prompt():
+            sl = m.seq_alloc()
+            m.batch_step([(sl, toks, [T - 1])])
+            m.seq_free(sl)
+        for _ in range(3):
+            prompt()
+        reps = max(3, args.steps // 16)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            prompt()
+        v[f"prompt{T}_tok_s"] = T / ((time.perf_counter() - t0) / reps)
+        m.profile(True)
+        prompt()
+        v[f"prompt{T}_device_ms"] = m.profile_ms()
+        m.profile(False)
+    for B in (1, 8):
+        slots = [m.seq_alloc() for _ in range(B)]
+        ctx = rng.integers(0, vocab, CTX).tolist()
+        m.batch_step([(sl, ctx, []) for sl in slots])
+        step = lambda: m.batch_step([(sl, [5], []) for sl in slots], greedy=True)   # noqa: E731
+        for _ in range(max(3, args.warmup)):
+            step()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step()
+        dt = (time.perf_counter() - t0) / args.steps
+        v[f"decode_b{B}_tok_s"] = B / dt
+        v[f"decode_b{B}_ms_per_step"] = dt * 1e3
+        m.profile(True)
+        step()
+        v[f"decode_b{B}_device_ms"] = m.profile_ms()
+        m.profile(False)
+        for sl in slots:
+            m.seq_free(sl)
+    return v
+
+
 def run_mumizen(args, pkg, lib):
     """Mumizen beside Vamidra at equal width / feed-forward / head size and six layer runs each: whole-model prompt and decode throughput
     through the public entry points, device time per kernel category, and for every pair of like kernels the distance from its roofline."""
@@ -308,47 +355,6 @@ def run_mumizen(args, pkg, lib):
     rng = np.random.default_rng(0)
     CTX = 1024
 
-    def measure(m, vocab):
-        v = {}
-        for T in (512, 2048):
-            toks = rng.integers(0, vocab, T).tolist()
-
-            def prompt():
-                sl = m.seq_alloc()
-                m.batch_step([(sl, toks, [T - 1])])
-                m.seq_free(sl)
-            for _ in range(3):
-                prompt()
-            reps = max(3, args.steps // 16)
-            t0 = time.perf_counter()
-            for _ in range(reps):
-                prompt()
-            v[f"prompt{T}_tok_s"] = T / ((time.perf_counter() - t0) / reps)
-            m.profile(True)
-            prompt()
-            v[f"prompt{T}_device_ms"] = m.profile_ms()
-            m.profile(False)
-        for B in (1, 8):
-            slots = [m.seq_alloc() for _ in range(B)]
-            ctx = rng.integers(0, vocab, CTX).tolist()
-            m.batch_step([(sl, ctx, []) for sl in slots])
-            step = lambda: m.batch_step([(sl, [5], []) for sl in slots], greedy=True)   # noqa: E731
-            for _ in range(max(3, args.warmup)):
-                step()
-            t0 = time.perf_counter()
-            for _ in range(args.steps):
-                step()
-            dt = (time.perf_counter() - t0) / args.steps
-            v[f"decode_b{B}_tok_s"] = B / dt
-            v[f"decode_b{B}_ms_per_step"] = dt * 1e3
-            m.profile(True)
-            step()
-            v[f"decode_b{B}_device_ms"] = m.profile_ms()
-            m.profile(False)
-            for sl in slots:
-                m.seq_free(sl)
-        return v
-
     for key in ([args.arch_size] if args.arch_size != "all" else list(SIZES)):
         s, z = SIZES[key], MUMIZEN_SIZES[key]
         W, V = s["width"], s["vocab"]
@@ -358,7 +364,7 @@ def run_mumizen(args, pkg, lib):
         m = pkg.Model.from_config(cfg, dtype="bfloat16", n_ctx=4096, n_seq=16)
         m.synth(0, 7)
         m.finalize()
-        a = measure(m, V)
+        a = measure(m, V, args, rng, CTX)
         m.close()
         H, D, Dv, Dr, R = z["heads"], z["dim"], z["vdim"], z["rot_dim"], z["kv_rank"]
         n_lin = sum(l["type"] != "latent_attention" for l in cfg["layers"])
@@ -388,7 +394,7 @@ def run_mumizen(args, pkg, lib):
         m = pkg.Model.from_config(vcfg, dtype="bfloat16", n_ctx=4096, n_seq=16)
         m.synth(0, 7)
         m.finalize()
-        b = measure(m, V)
+        b = measure(m, V, args, rng, CTX)
         m.close()
         shapes = dense_shapes(s, vcfg)
         for T in (512, 2048):
@@ -407,6 +413,135 @@ def run_mumizen(args, pkg, lib):
             b[f"decode_b{B}_attention_gbs"] = 3 * B * rows * s["kv_heads"] * 2 * s["dim"] * 4.0 / pm["attention"] / 1e6
             b[f"decode_b{B}_whole_step_frac_of_hbm_peak"] = b["weight_bytes_per_token"] / b[f"decode_b{B}_ms_per_step"] / 1e6 / hbm
         out["vamidra"] = b
+        res["sizes"][key] = out
+        torch.cuda.empty_cache()
+    res["gpu_launches"] = int(lib.c.pb200_kernel_launches())
+    print(json.dumps(res))
+    return res
+
+
+# ---------------------------------------------------------------------------------------------------------------
+SAPUDRA_SIZES = {
+    "w2048": dict(experts=16, top=2, expert_ff=2048, shared_ff=2048, count=4, keep=2),
+    "w4096": dict(experts=16, top=2, expert_ff=4096, shared_ff=4096, count=4, keep=2),
+}
+
+
+def sapudra_config(s, z):
+    """Six attention layers at the width / feed-forward / head sizes of SIZES (window as Vamidra's, no kept first tokens): four dense
+    squared-ReLU feed-forwards and two mixtures of experts with a gated shared expert."""
+    att = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5, "mask": {"size": s["window"]}}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "shared": {"ff": z["shared_ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5, "groups": {"count": z["count"], "keep": z["keep"]}}}
+    layers = [{"type": "attention", "mixer": att, "mlp": f} for f in (dense, moe, dense, moe, dense, dense)]
+    return {"architecture": "Sapudra", "width": s["width"], "vocab": s["vocab"], "max_positions": 4096, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "logit_softcap": 30.0, "layers": layers}
+
+
+def sapudra_products(cfg):
+    """((N, K) of the plain dense products, expert weight elements touched) of one token through all layers, the head not included."""
+    W, out, expert = cfg["width"], [], 0
+    for l in cfg["layers"]:
+        m = l["mixer"]
+        out += [(m["heads"] * m["dim"] + m["kv_heads"] * (m["dim"] + m["vdim"]), W), (W, m["heads"] * m["vdim"])]
+        f = l["mlp"]
+        if f["kind"] == "dense":
+            out += [(f["ff"], W), (W, f["ff"])]
+        else:
+            out += [(f["shared"]["ff"], W), (W, f["shared"]["ff"])]
+            expert += f["router"]["top"] * 2 * f["expert"]["ff"] * W
+    return out, expert
+
+
+def run_sapudra(args, pkg, lib):
+    """Sapudra beside Vamidra (attention, plain products, norms, element-wise steps: the same or like kernels) and beside Mumizen (expert
+    products) at equal width / feed-forward / head size and six layer runs each: whole-model prompt and decode throughput through the
+    public entry points, device time per kernel category, and for every pair of like kernels the distance from its roofline."""
+    import numpy as np
+    import torch
+    hbm, tflops, src = peaks()
+    res = {"metric": "Sapudra prompt / decode throughput beside Vamidra and Mumizen at equal size", "impl": "b200", "arch": "Sapudra", "n_gpus": 1,
+           "dtype": "bf16", "data": "synthetic random weights", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": src}, "sizes": {}}
+    rng = np.random.default_rng(0)
+    CTX = 1024
+
+    def model(cfg):
+        m = pkg.Model.from_config(cfg, dtype="bfloat16", n_ctx=4096, n_seq=16)
+        m.synth(0, 7)
+        m.finalize()
+        return m
+
+    for key in ([args.arch_size] if args.arch_size != "all" else list(SIZES)):
+        s, z = SIZES[key], SAPUDRA_SIZES[key]
+        W, V, H, G, D = s["width"], s["vocab"], s["heads"], s["kv_heads"], s["dim"]
+        out = {"config": dict(z, width=W, ff=s["ff"], heads=H, kv_heads=G, dim=D, window=s["window"], vocab=V), "layers": 6}
+        # ---------------- the new design ----------------
+        cfg = sapudra_config(s, z)
+        m = model(cfg)
+        a = measure(m, V, args, rng, CTX)
+        m.close()
+        prods, expert = sapudra_products(cfg)
+        n_moe = sum(l["mlp"]["kind"] == "moe" for l in cfg["layers"])
+        for T in (512, 2048):
+            pm = a[f"prompt{T}_device_ms"]
+            a[f"prompt{T}_dense_frac_of_tensor_peak"] = 2.0 * sum(n * k for n, k in prods) * T / pm["dense"] / 1e9 / tflops
+            a[f"prompt{T}_experts_frac_of_tensor_peak"] = 2.0 * expert * T / pm["experts"] / 1e9 / tflops
+            vis = sum(min(i + 1, s["window"]) for i in range(T))
+            a[f"prompt{T}_attention_tflops"] = 6 * 4.0 * D * H * vis / pm["attention"] / 1e9
+            # 12 post-norms: the sublayer result and x read, x and the operand written
+            a[f"prompt{T}_norm_gbs"] = 12 * T * W * 14.0 / pm["norm"] / 1e6
+            # squared ReLU: 4 dense + 2 shared hidden rows read (fp32) and written (bf16); embedding: table rows read, x and operand written
+            elem = T * 6.0 * (4 * s["ff"] + n_moe * z["shared_ff"]) + T * W * 10.0
+            a[f"prompt{T}_elementwise_gbs"] = elem / pm["elementwise"] / 1e6
+        wb = 2.0 * sum(n * k for n, k in prods)
+        a["weight_bytes_per_token"] = wb + 2.0 * expert + 2.0 * V * W
+        rows = min(CTX, s["window"])
+        for B in (1, 8):
+            pm = a[f"decode_b{B}_device_ms"]
+            a[f"decode_b{B}_dense_frac_of_hbm_peak"] = wb / pm["dense"] / 1e6 / hbm
+            a[f"decode_b{B}_experts_frac_of_hbm_peak"] = 2.0 * expert * B / pm["experts"] / 1e6 / hbm     # b = 8: the most bytes the 8 tokens can touch
+            a[f"decode_b{B}_attention_gbs"] = 6 * B * rows * G * 2 * D * 4.0 / pm["attention"] / 1e6
+            a[f"decode_b{B}_whole_step_frac_of_hbm_peak"] = a["weight_bytes_per_token"] / a[f"decode_b{B}_ms_per_step"] / 1e6 / hbm
+        out["sapudra"] = a
+        # ---------------- the closest existing model: Vamidra, equal sizes, 6 layer runs ----------------
+        vcfg = vamidra_config(s)
+        m = model(vcfg)
+        b = measure(m, V, args, rng, CTX)
+        m.close()
+        shapes = dense_shapes(s, vcfg)
+        for T in (512, 2048):
+            pm = b[f"prompt{T}_device_ms"]
+            b[f"prompt{T}_dense_frac_of_tensor_peak"] = 2.0 * sum(n * k for n, k in shapes) * T / pm["dense"] / 1e9 / tflops
+            vis = sum(min(i + 1, s["window"]) + max(0, min(s["keep_first"], i + 1 - s["window"])) for i in range(T))
+            b[f"prompt{T}_attention_tflops"] = 3 * 4.0 * D * H * vis / pm["attention"] / 1e9
+            b[f"prompt{T}_norm_gbs"] = (12 * T * W * 6.0 + 3 * T * s["ssm_heads"] * s["vdim"] * 10.0) / pm["norm"] / 1e6
+            # tanh-GELU gating: 6 hidden rows of gate | up read (fp32), the product written (bf16); embedding; input mix casts
+            b[f"prompt{T}_elementwise_gbs"] = (T * 10.0 * 6 * s["ff"] + T * W * 12.0 + 2 * 2 * T * W * 6.0) / pm["elementwise"] / 1e6
+        wbv = 2.0 * sum(n * k for n, k in shapes)
+        b["weight_bytes_per_token"] = wbv + 2.0 * V * W
+        vrows = min(CTX, s["window"] + s["keep_first"])
+        for B in (1, 8):
+            pm = b[f"decode_b{B}_device_ms"]
+            b[f"decode_b{B}_dense_frac_of_hbm_peak"] = wbv / pm["dense"] / 1e6 / hbm
+            b[f"decode_b{B}_attention_gbs"] = 3 * B * vrows * G * 2 * D * 4.0 / pm["attention"] / 1e6
+            b[f"decode_b{B}_whole_step_frac_of_hbm_peak"] = b["weight_bytes_per_token"] / b[f"decode_b{B}_ms_per_step"] / 1e6 / hbm
+        out["vamidra"] = b
+        # ---------------- the closest existing experts: Mumizen at equal expert sizes ----------------
+        mz = dict(MUMIZEN_SIZES[key], experts=z["experts"], top=z["top"], expert_ff=z["expert_ff"], shared_ff=z["shared_ff"])
+        mcfg = mumizen_config(s, mz)
+        m = model(mcfg)
+        c = measure(m, V, args, rng, CTX)
+        m.close()
+        _, mexpert = mumizen_products(mcfg, True)
+        e = {}
+        for T in (512, 2048):
+            e[f"prompt{T}_experts_frac_of_tensor_peak"] = 2.0 * mexpert * T / c[f"prompt{T}_device_ms"]["experts"] / 1e9 / tflops
+            e[f"prompt{T}_experts_ms"] = c[f"prompt{T}_device_ms"]["experts"]
+        for B in (1, 8):
+            e[f"decode_b{B}_experts_frac_of_hbm_peak"] = 2.0 * mexpert * B / c[f"decode_b{B}_device_ms"]["experts"] / 1e6 / hbm
+            e[f"decode_b{B}_experts_ms"] = c[f"decode_b{B}_device_ms"]["experts"]
+        out["mumizen_experts"] = e
         res["sizes"][key] = out
         torch.cuda.empty_cache()
     res["gpu_launches"] = int(lib.c.pb200_kernel_launches())

@@ -104,6 +104,27 @@ def route(h, W, pre, r):
     return idx, wts
 
 
+def route_margin(h, W, pre, r):
+    """Per token: the smallest gap that decides the choice, i.e. between the last chosen and the best not chosen eligible choice score, and
+    between the last kept and the best dropped group score.  A token with a small margin may be routed differently after rounding."""
+    E, top = r["experts"], r["top"]
+    gr = r.get("groups") or {"count": 1, "keep": 1}
+    ng, keep = gr["count"], gr["keep"]
+    choice = sigmoid(h @ W[pre + "router"].T) + W[pre + "correction"]
+    per = E // ng
+    out = np.full(h.shape[0], np.inf)
+    for t in range(h.shape[0]):
+        cg = choice[t].reshape(ng, per)
+        gscore = np.sort(np.sort(cg, axis=-1)[:, -2:].sum(-1))[::-1]
+        if keep < ng:
+            out[t] = min(out[t], gscore[keep - 1] - gscore[keep])
+        best = np.argsort(-np.sort(cg, axis=-1)[:, -2:].sum(-1), kind="stable")[:keep]
+        elig = np.sort(np.concatenate([cg[g] for g in best]))[::-1]
+        if top < len(elig):
+            out[t] = min(out[t], elig[top - 1] - elig[top])
+    return out
+
+
 def mixture(h, W, pre, mlp):
     idx, wts = route(h, W, pre, mlp["router"])
     y = np.zeros((h.shape[0], W[pre + "e0.down"].shape[0]))
@@ -122,8 +143,9 @@ def feed_forward(h, W, pre, mlp):
 
 
 # ---- the model ----
-def forward(cfg, W, tokens):
-    """logits [T, vocab] and the stream that leaves every layer [layers, T, width], for one sequence from position 0."""
+def forward(cfg, W, tokens, margins=None):
+    """logits [T, vocab] and the stream that leaves every layer [layers, T, width], for one sequence from position 0.  margins: a list
+    that receives one array [T] per mixture layer, the routing margin of every token there (route_margin)."""
     eps, m = cfg["norm"]["eps"], cfg.get("residual_mult", 1.0)
     x = embed(W, tokens)
     taps = []
@@ -132,6 +154,8 @@ def forward(cfg, W, tokens):
         assert l["type"] == "attention"
         x = x + m * layer_norm(window_attention(x, W, p + "mix.", l["mixer"], eps), W[p + "norm1"], W[p + "norm1.b"], eps)
         if l.get("mlp"):
+            if margins is not None and l["mlp"]["kind"] == "moe":
+                margins.append(route_margin(x, W, p + "mlp.", l["mlp"]["router"]))
             x = x + m * layer_norm(feed_forward(x, W, p + "mlp.", l["mlp"]), W[p + "norm2"], W[p + "norm2.b"], eps)
         taps.append(x)
     x = layer_norm(x, W["final.norm"], W["final.norm.b"], eps)
