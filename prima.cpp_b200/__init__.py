@@ -4,8 +4,9 @@ The product is ``libprima_b200.so`` (CUDA kernels + C++ decode engine, ``include
 ``libggml-b200.so`` (the same kernels behind the reference's ggml-backend vtables, ``include/ggml_b200.h``).
 The same library and model object serve a second family of models, the layer list: dense bf16 / f32 weights from a safetensors
 directory, sequence slots and a ragged batch step (``Model.from_dir`` / ``Model.batch_step``), driven by :class:`BatchScheduler`.
-Designs: Vamidra (windowed attention with kept first tokens, Mamba-2 mixers) and Mumizen (decay linear attention, attention over a
-low-rank latent, clamped gated feed-forward and mixtures of experts, token shift, depth average).
+Designs: Vamidra (windowed attention with kept first tokens, Mamba-2 mixers), Mumizen (decay linear attention, attention over a
+low-rank latent, clamped gated feed-forward and mixtures of experts, token shift, depth average) and Sapudra (post-norm layers with a
+position table, windowed attention with normed query / key heads, squared-ReLU feed-forward, router with sigmoid scores and expert groups).
 This Python package is only the thin ctypes binding plus the schedulers; it never falls back to a CPU path: importing
 :mod:`host` raises if the CUDA library is missing.
 """
