@@ -154,7 +154,7 @@ struct LayerList {
     void *act = nullptr, *act2 = nullptr, *actw = nullptr;
     // FRAME_PRENORM and its mixers: results of all layers [layers + 1][capT][width]; further fp32 and operand-type scratch
     float *hist = nullptr, *big2 = nullptr, *big3 = nullptr, *big4 = nullptr, *krb = nullptr;
-    float * lat_part = nullptr;     // partial results of the split latent decode attention, [entries][splits][heads][kv_rank + 2]
+    float * lat_part = nullptr;     // partial results of the split decode attention kernels: latent [entries][splits][heads][kv_rank + 2], windowed [entries][heads][splits][vdim + 2]
     size_t lat_part_cap = 0;
     // mixture of experts: pairs (token, choice)
     int32_t *moe_idx = nullptr, *moe_perm = nullptr, *moe_row_of = nullptr, *moe_count = nullptr, *moe_start = nullptr, *moe_count_host = nullptr;
@@ -1030,6 +1030,8 @@ static int ll_reserve(pb200_model * m, int T, int nW, int nE) {
     for (const LLayer & L : ll.layers)
         if (L.kind == MIX_LATENT)
             need_part = std::max(need_part, (size_t) nE * (size_t) latent_decode_splits(ll.n_ctx) * (size_t) L.lat.heads * (size_t) (L.lat.kv_rank + 2));
+        else if (L.kind == MIX_ATTENTION)
+            need_part = std::max(need_part, attn_decode_part_floats(L.att, nE));
     if (need_part > ll.lat_part_cap) {
         CK(cudaStreamSynchronize(m->stream));
         ll_drop_graphs(ll);
@@ -1105,7 +1107,7 @@ static int mix_attention(pb200_model * m, const BatchView & b, bool prefill, con
     if (L.qk_norm) CK(launch_attn_qknorm_kv_store(ll.big, b, a, L.q_norm.data, L.k_norm.data, ll.eps, kc, vc, ll.slot_floats, st));
     else CK(launch_attn_kv_store(ll.big, b, a, kc, vc, ll.slot_floats, st));
     if (prefill) CK(launch_attn_window_prefill(ll.big, b, a, ll.act, ct, st));
-    else CK(launch_attn_window_decode(ll.big, b, a, kc, vc, ll.slot_floats, ll.act, ct, st));
+    else CK(launch_attn_window_decode(ll.big, b, a, kc, vc, ll.slot_floats, ll.act, ct, st, ll.lat_part));
     CAT(CAT_DENSE);
     return launch_dense(ct, ll.act, (int64_t) a.heads * a.vdim, L.out.data, (int64_t) a.heads * a.vdim, out, W, T, W, a.heads * a.vdim, nullptr, resid, W, 1.f, st);
 }

@@ -112,14 +112,24 @@ int launch_attn_qknorm_kv_store(float * qkvg, const BatchView & b, const AttnPar
                                 float * vcache, int64_t slot_stride, cudaStream_t stream);
 // entries that start at position 0: keys and values are read from the batch itself
 int launch_attn_window_prefill(const float * qkvg, const BatchView & b, const AttnParams & a, void * out, int otype, cudaStream_t stream);
-// one-token entries: keys and values come from the cache (the token's own row already stored)
+// one-token entries: keys and values come from the cache (the token's own row already stored).  part (may be null): scratch of
+// attn_decode_part_floats floats; with it and a cache of 128 rows or more the rows are split over several CTAs per (head, entry) in chunks
+// of attn_decode_chunk rows, and a second kernel merges the partial softmax states.  The split depends on the cache's row count alone.
+inline int attn_decode_chunk(int cache_rows) {
+    const int c = (cache_rows + 63) / 64;                 // at most 64 splits ...
+    return c < 64 ? 64 : (c + 31) / 32 * 32;              // ... of at least 64 rows
+}
+inline int attn_decode_splits(int cache_rows) { return cache_rows < 128 ? 1 : (cache_rows + attn_decode_chunk(cache_rows) - 1) / attn_decode_chunk(cache_rows); }
+inline size_t attn_decode_part_floats(const AttnParams & a, int n_entries) {
+    return (size_t) n_entries * (size_t) a.heads * (size_t) attn_decode_splits(a.cache_rows) * (size_t) (a.vdim + 2);
+}
 int launch_attn_window_decode(const float * qkvg, const BatchView & b, const AttnParams & a, const float * kcache, const float * vcache,
-                              int64_t slot_stride, void * out, int otype, cudaStream_t stream);
+                              int64_t slot_stride, void * out, int otype, cudaStream_t stream, float * part = nullptr);
 
 // the same two kernels with every input given by an AttnIO
 int launch_attn_prefill_io(const AttnIO & io, const BatchView & b, const AttnParams & a, void * out, int otype, cudaStream_t stream);
 int launch_attn_decode_io(const AttnIO & io, const BatchView & b, const AttnParams & a, const float * kcache, const float * vcache, int64_t slot_stride,
-                          void * out, int otype, cudaStream_t stream);
+                          void * out, int otype, cudaStream_t stream, float * part = nullptr);
 
 // ---- Mamba-2 ----
 struct Mamba2Params {

@@ -471,15 +471,18 @@ __global__ void __launch_bounds__(256) k_attn_window_prefill_tiled(const AttnIO 
     }
 }
 
-// decode: one CTA of 32 warps per (head, entry).  Warp w takes cache rows 4 w .. 4 w + 3, then 128 further on, ...: the lanes split the key's
-// dimensions (coalesced row reads, four rows in flight), the score is a warp sum, the running max / sum are uniform over the warp, and every lane accumulates its share of the value
-// dimensions.  The 32 partial softmax states are merged in shared memory.
-constexpr int DEC_WARPS = 32, DEC_ROWS = 4;
+// decode: CTA (head, entry, split).  Warp w takes cache rows 4 w .. 4 w + 3 of the split's chunk, then 4 * warps further on, ...: the lanes
+// split the key's dimensions (coalesced row reads, four rows in flight), the score is a warp sum, the running max / sum are uniform over the
+// warp, and every lane accumulates its share of the value dimensions.  The warps' partial softmax states are merged in shared memory.  With
+// one split (32 warps over all rows) the CTA writes the output; with several (8 warps over `chunk` rows each) it writes its partial state
+// [max, sum, weighted values] and k_attn_decode_merge finishes.  The number of splits comes from the cache's row count alone (the layer's
+// window and the context size), so a sequence's result does not depend on the batch around it.
+constexpr int DEC_WARPS = 32, DEC_ROWS = 4, DEC_SPLIT_WARPS = 8;
 template <typename OT, int NV>
 __global__ void __launch_bounds__(DEC_WARPS * 32) k_attn_window_decode(const AttnIO io, const int32_t * __restrict__ slot,
                                                                        const int32_t * __restrict__ off, const int32_t * __restrict__ pos0, AttnParams a,
                                                                        const float * __restrict__ kcache, const float * __restrict__ vcache,
-                                                                       int64_t slot_stride, OT * __restrict__ out) {
+                                                                       int64_t slot_stride, OT * __restrict__ out, float * __restrict__ part, int chunk) {
     extern __shared__ float sm[];
     const int e = blockIdx.y, h = blockIdx.x;
     const int t = off[e];
@@ -489,9 +492,10 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) k_attn_window_decode(const Att
     const int kvh = h / (a.heads / a.kv_heads);
     const int64_t KD = io.k_row, VD = io.v_row;
     const int keep = min(a.keep_first, a.cache_rows), ring = a.cache_rows - keep;
+    const int nw = blockDim.x >> 5;
     float * qs = sm;                       // [D], scaled
-    float * mm = qs + ((D + 3) & ~3);      // [DEC_WARPS] max, [DEC_WARPS] sum
-    float * accs = mm + 2 * DEC_WARPS;     // [DEC_WARPS][NV*32]
+    float * mm = qs + ((D + 3) & ~3);      // [nw] max, [nw] sum
+    float * accs = mm + 2 * nw;            // [nw][NV*32]
     for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = io.q[(int64_t) t * io.ldq + h * D + d] * a.scale;
     __syncthreads();
     const float * kc = kcache + (int64_t) slot[e] * slot_stride, * vc = vcache + (int64_t) slot[e] * slot_stride;
@@ -499,18 +503,19 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) k_attn_window_decode(const Att
 #pragma unroll
     for (int c = 0; c < NV; c++) acc[c] = 0.f;
     const int rows_used = min(a.cache_rows, pi + 1);
+    const int r_begin = gridDim.z > 1 ? blockIdx.z * chunk : 0, r_end = gridDim.z > 1 ? min(rows_used, r_begin + chunk) : rows_used;
     const bool vec4 = (D & 3) == 0 && (KD & 3) == 0;
-    for (int r0 = warp * DEC_ROWS; r0 < rows_used; r0 += DEC_WARPS * DEC_ROWS) {
+    for (int r0 = r_begin + warp * DEC_ROWS; r0 < r_end; r0 += nw * DEC_ROWS) {
         // DEC_ROWS rows per step so that their loads are in flight together; which position does row r hold right now?
         float sc[DEC_ROWS];
 #pragma unroll
         for (int j = 0; j < DEC_ROWS; j++) {
             const int r = r0 + j;
             int p = -1;
-            if (r < rows_used) {
+            if (r < r_end) {
                 if (r < keep) p = r;
                 else {
-                    const int rr = r - keep, ip = pi - keep;       // ip >= 0 here because r < rows_used <= pi + 1
+                    const int rr = r - keep, ip = pi - keep;       // ip >= 0 here because r < r_end <= rows_used <= pi + 1
                     p = keep + ip - ((ip - rr) % ring + ring) % ring;
                     if (p < keep) p = -1;
                 }
@@ -559,22 +564,32 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) k_attn_window_decode(const Att
         }
         m = mn;
     }
-    if (lane == 0) { mm[warp] = m; mm[DEC_WARPS + warp] = l; }
+    if (lane == 0) { mm[warp] = m; mm[nw + warp] = l; }
 #pragma unroll
     for (int c = 0; c < NV; c++) accs[warp * NV * 32 + c * 32 + lane] = acc[c];
     __syncthreads();
     if (warp == 0) {
         float M = -INFINITY;
-        for (int w = 0; w < DEC_WARPS; w++) M = fmaxf(M, mm[w]);
+        for (int w = 0; w < nw; w++) M = fmaxf(M, mm[w]);
         float L = 0.f, o[NV];
 #pragma unroll
         for (int c = 0; c < NV; c++) o[c] = 0.f;
-        for (int w = 0; w < DEC_WARPS; w++) {
+        for (int w = 0; w < nw; w++) {
             if (mm[w] == -INFINITY) continue;
             const float f = expf(mm[w] - M);
-            L += mm[DEC_WARPS + w] * f;
+            L += mm[nw + w] * f;
 #pragma unroll
             for (int c = 0; c < NV; c++) o[c] = fmaf(accs[w * NV * 32 + c * 32 + lane], f, o[c]);
+        }
+        if (gridDim.z > 1) {   // partial state of this split
+            float * pp = part + (((int64_t) e * a.heads + h) * gridDim.z + blockIdx.z) * (DV + 2);
+            if (lane == 0) { pp[0] = M; pp[1] = L; }
+#pragma unroll
+            for (int c = 0; c < NV; c++) {
+                const int d = lane + 32 * c;
+                if (d < DV) pp[2 + d] = o[c];
+            }
+            return;
         }
         const float inv = L > 0.f ? 1.f / L : 0.f;
 #pragma unroll
@@ -582,6 +597,31 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) k_attn_window_decode(const Att
             const int d = lane + 32 * c;
             if (d < DV) put(out, (int64_t) t * (a.heads * DV) + h * DV + d, o[c] * inv * attn_gate(io, t, h, d, DV));
         }
+    }
+}
+
+// merges the partial softmax states of a (head, entry): grid (heads, entries), one thread per value dimension
+template <typename OT>
+__global__ void __launch_bounds__(128) k_attn_decode_merge(const AttnIO io, const int32_t * __restrict__ off, AttnParams a, const float * __restrict__ part,
+                                                           int splits, OT * __restrict__ out) {
+    const int e = blockIdx.y, h = blockIdx.x, DV = a.vdim;
+    const int t = off[e];
+    const float * pp = part + ((int64_t) e * a.heads + h) * splits * (DV + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < splits; s++) M = fmaxf(M, pp[(int64_t) s * (DV + 2)]);
+    float L = 0.f;
+    for (int s = 0; s < splits; s++) {
+        const float ms = pp[(int64_t) s * (DV + 2)];
+        if (ms != -INFINITY) L += pp[(int64_t) s * (DV + 2) + 1] * expf(ms - M);
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    for (int d = threadIdx.x; d < DV; d += blockDim.x) {
+        float o = 0.f;
+        for (int s = 0; s < splits; s++) {
+            const float ms = pp[(int64_t) s * (DV + 2)];
+            if (ms != -INFINITY) o = fmaf(pp[(int64_t) s * (DV + 2) + 2 + d], expf(ms - M), o);
+        }
+        put(out, (int64_t) t * (a.heads * DV) + h * DV + d, o * inv * attn_gate(io, t, h, d, DV));
     }
 }
 
@@ -924,20 +964,27 @@ int launch_attn_prefill_io(const AttnIO & io, const BatchView & b, const AttnPar
 }
 template <typename OT, int NV>
 static int attn_decode_typed(const AttnIO & io, const BatchView & b, const AttnParams & a, const float * kc, const float * vc, int64_t stride, OT * out,
-                             cudaStream_t st) {
-    const size_t smem = ((size_t) ((a.dim + 3) & ~3) + 2 * DEC_WARPS + (size_t) DEC_WARPS * NV * 32) * sizeof(float);
-    int rc = raise_smem(k_attn_window_decode<OT, NV>, smem);
+                             float * part, cudaStream_t st) {
+    const int splits = part ? attn_decode_splits(a.cache_rows) : 1;
+    const int nw = splits > 1 ? DEC_SPLIT_WARPS : DEC_WARPS;
+    const size_t smem = ((size_t) ((a.dim + 3) & ~3) + 2 * nw + (size_t) nw * NV * 32) * sizeof(float);
+    int rc = raise_smem(k_attn_window_decode<OT, NV>, ((size_t) ((a.dim + 3) & ~3) + 2 * DEC_WARPS + (size_t) DEC_WARPS * NV * 32) * sizeof(float));
     if (rc) return rc;
-    const dim3 grid((unsigned) a.heads, (unsigned) b.n_entries);
-    return ck_launch([&] { k_attn_window_decode<OT, NV><<<grid, DEC_WARPS * 32, smem, st>>>(io, b.slot, b.off, b.pos0, a, kc, vc, stride, out); });
+    const dim3 grid((unsigned) a.heads, (unsigned) b.n_entries, (unsigned) splits);
+    rc = ck_launch([&] {
+        k_attn_window_decode<OT, NV><<<grid, nw * 32, smem, st>>>(io, b.slot, b.off, b.pos0, a, kc, vc, stride, out, part, attn_decode_chunk(a.cache_rows));
+    });
+    if (rc || splits == 1) return rc;
+    const dim3 mgrid((unsigned) a.heads, (unsigned) b.n_entries);
+    return ck_launch([&] { k_attn_decode_merge<OT><<<mgrid, 128, 0, st>>>(io, b.off, a, part, splits, out); });
 }
 int launch_attn_decode_io(const AttnIO & io, const BatchView & b, const AttnParams & a, const float * kcache, const float * vcache, int64_t slot_stride,
-                          void * out, int otype, cudaStream_t st) {
+                          void * out, int otype, cudaStream_t st, float * part) {
     if (b.n_tokens <= 0) return 0;
     if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads != 0 || a.dim <= 0 || a.vdim <= 0) return (int) cudaErrorInvalidValue;
     const int nv = (a.vdim + 31) / 32;
-    if (otype == T_BF16) PB_NV_DISPATCH(nv, return (attn_decode_typed<__nv_bfloat16, NV>(io, b, a, kcache, vcache, slot_stride, (__nv_bfloat16 *) out, st)));
-    else PB_NV_DISPATCH(nv, return (attn_decode_typed<float, NV>(io, b, a, kcache, vcache, slot_stride, (float *) out, st)));
+    if (otype == T_BF16) PB_NV_DISPATCH(nv, return (attn_decode_typed<__nv_bfloat16, NV>(io, b, a, kcache, vcache, slot_stride, (__nv_bfloat16 *) out, part, st)));
+    else PB_NV_DISPATCH(nv, return (attn_decode_typed<float, NV>(io, b, a, kcache, vcache, slot_stride, (float *) out, part, st)));
     return 0;
 }
 
@@ -957,8 +1004,8 @@ int launch_attn_window_prefill(const float * qkvg, const BatchView & b, const At
     return launch_attn_prefill_io(attn_io_fused(qkvg, a), b, a, out, otype, st);
 }
 int launch_attn_window_decode(const float * qkvg, const BatchView & b, const AttnParams & a, const float * kcache, const float * vcache, int64_t slot_stride,
-                              void * out, int otype, cudaStream_t st) {
-    return launch_attn_decode_io(attn_io_fused(qkvg, a), b, a, kcache, vcache, slot_stride, out, otype, st);
+                              void * out, int otype, cudaStream_t st, float * part) {
+    return launch_attn_decode_io(attn_io_fused(qkvg, a), b, a, kcache, vcache, slot_stride, out, otype, st, part);
 }
 
 int launch_mamba2_conv(const float * u, const BatchView & b, const Mamba2Params & p, const float * w, const float * bias, float * conv_state,
