@@ -104,37 +104,46 @@ template <int N> __device__ __forceinline__ void unpack(const uint4 & raw, float
     }
 }
 
+// KS warps share a weight row (each takes a contiguous part of K, a multiple of the 16-byte load step; the parts are summed in order
+// through shared memory): matrices with few, long rows keep more loads in flight that way.  KS comes from (N, K) alone.
 template <typename WT, int TB, bool VEC>
 __global__ void __launch_bounds__(256) k_dense_rows(const WT * __restrict__ A, int64_t lda, const WT * __restrict__ W, int64_t ldw, float * C, int64_t ldc,
-                                                    int T, int N, int K, const float * __restrict__ bias, const float * resid, int64_t ldr, float alpha) {
-    const int lane = threadIdx.x & 31;
-    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (n >= N) return;
-    const WT * w = W + (int64_t) n * ldw;
+                                                    int T, int N, int K, const float * __restrict__ bias, const float * resid, int64_t ldr, float alpha,
+                                                    int KS) {
+    __shared__ float parts[8][TB];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rows_per_cta = (blockDim.x >> 5) / KS;
+    const int n = blockIdx.x * rows_per_cta + warp / KS, part = warp % KS;
+    const bool live = n < N;
+    constexpr int V = Vec16<WT>::n;
+    const int Kc = KS == 1 ? K : ((K + KS - 1) / KS + 32 * V - 1) / (32 * V) * (32 * V);
+    const int k_begin = part * Kc, k_end = min(K, k_begin + Kc);
+    const WT * w = W + (int64_t) (live ? n : 0) * ldw;
     float acc[TB];
 #pragma unroll
     for (int t = 0; t < TB; t++) acc[t] = 0.f;
-    if (VEC) {
-        constexpr int V = Vec16<WT>::n;
-        for (int k = lane * V; k < K; k += 32 * V) {
-            float wf[V];
-            unpack<V>(__ldcs(reinterpret_cast<const uint4 *>(w + k)), wf, WT());   // streamed once: do not keep in L1
+    if (live) {
+        if (VEC) {
+            for (int k = k_begin + lane * V; k < k_end; k += 32 * V) {
+                float wf[V];
+                unpack<V>(__ldcs(reinterpret_cast<const uint4 *>(w + k)), wf, WT());   // streamed once: do not keep in L1
 #pragma unroll
-            for (int t = 0; t < TB; t++) {
-                if (t < T) {
-                    float af[V];
-                    unpack<V>(__ldg(reinterpret_cast<const uint4 *>(A + (int64_t) t * lda + k)), af, WT());
+                for (int t = 0; t < TB; t++) {
+                    if (t < T) {
+                        float af[V];
+                        unpack<V>(__ldg(reinterpret_cast<const uint4 *>(A + (int64_t) t * lda + k)), af, WT());
 #pragma unroll
-                    for (int i = 0; i < V; i++) acc[t] = fmaf(af[i], wf[i], acc[t]);
+                        for (int i = 0; i < V; i++) acc[t] = fmaf(af[i], wf[i], acc[t]);
+                    }
                 }
             }
-        }
-    } else {
-        for (int k = lane; k < K; k += 32) {
-            const float wv = to_f(w[k]);
+        } else {
+            for (int k = k_begin + lane; k < k_end; k += 32) {
+                const float wv = to_f(w[k]);
 #pragma unroll
-            for (int t = 0; t < TB; t++)
-                if (t < T) acc[t] = fmaf(to_f(A[(int64_t) t * lda + k]), wv, acc[t]);
+                for (int t = 0; t < TB; t++)
+                    if (t < T) acc[t] = fmaf(to_f(A[(int64_t) t * lda + k]), wv, acc[t]);
+            }
         }
     }
 #pragma unroll
@@ -142,11 +151,31 @@ __global__ void __launch_bounds__(256) k_dense_rows(const WT * __restrict__ A, i
         float v = acc[t];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0 && t < T) {
-            v *= alpha;
-            if (bias) v += bias[n];
-            if (resid) v += resid[(int64_t) t * ldr + n];
-            C[(int64_t) t * ldc + n] = v;
+        acc[t] = v;
+    }
+    if (KS > 1) {
+        if (lane == 0) {
+#pragma unroll
+            for (int t = 0; t < TB; t++) parts[warp][t] = acc[t];
+        }
+        __syncthreads();
+        if (part != 0) return;
+#pragma unroll
+        for (int t = 0; t < TB; t++) {
+            float v = 0.f;
+            for (int j = 0; j < KS; j++) v += parts[warp + j][t];
+            acc[t] = v;
+        }
+    }
+    if (lane == 0 && live) {
+#pragma unroll
+        for (int t = 0; t < TB; t++) {
+            if (t < T) {
+                float v = acc[t] * alpha;
+                if (bias) v += bias[n];
+                if (resid) v += resid[(int64_t) t * ldr + n];
+                C[(int64_t) t * ldc + n] = v;
+            }
         }
     }
 }
@@ -170,17 +199,20 @@ int dense_typed(const WT * A, int64_t lda, const WT * W, int64_t ldw, float * C,
     if (T <= ROWS_MAX_T) {
         constexpr int V = Vec16<WT>::n;
         const bool vec = K % V == 0 && lda % V == 0 && ldw % V == 0 && ((uintptr_t) A & 15) == 0 && ((uintptr_t) W & 15) == 0;
-        const dim3 grid((unsigned) ((N + 7) / 8)), block(256);
+        // warps per row: few rows leave most of the machine's load slots empty, so 2, 4 or 8 warps split a long row
+        int KS = 1;
+        while (KS < 8 && (int64_t) N * KS < 6144 && K / (2 * KS) >= 1024) KS *= 2;
+        const dim3 grid((unsigned) ((N + 8 / KS - 1) / (8 / KS))), block(256);
         g_launches++;
         if (T <= 1) {
-            if (vec) k_dense_rows<WT, 1, true><<<grid, block, 0, st>>>(A, lda, W, ldw, C, ldc, T, N, K, bias, resid, ldr, alpha);
-            else k_dense_rows<WT, 1, false><<<grid, block, 0, st>>>(A, lda, W, ldw, C, ldc, T, N, K, bias, resid, ldr, alpha);
+            if (vec) k_dense_rows<WT, 1, true><<<grid, block, 0, st>>>(A, lda, W, ldw, C, ldc, T, N, K, bias, resid, ldr, alpha, KS);
+            else k_dense_rows<WT, 1, false><<<grid, block, 0, st>>>(A, lda, W, ldw, C, ldc, T, N, K, bias, resid, ldr, alpha, KS);
         } else if (T <= 4) {
-            if (vec) k_dense_rows<WT, 4, true><<<grid, block, 0, st>>>(A, lda, W, ldw, C, ldc, T, N, K, bias, resid, ldr, alpha);
-            else k_dense_rows<WT, 4, false><<<grid, block, 0, st>>>(A, lda, W, ldw, C, ldc, T, N, K, bias, resid, ldr, alpha);
+            if (vec) k_dense_rows<WT, 4, true><<<grid, block, 0, st>>>(A, lda, W, ldw, C, ldc, T, N, K, bias, resid, ldr, alpha, KS);
+            else k_dense_rows<WT, 4, false><<<grid, block, 0, st>>>(A, lda, W, ldw, C, ldc, T, N, K, bias, resid, ldr, alpha, KS);
         } else {
-            if (vec) k_dense_rows<WT, ROWS_MAX_T, true><<<grid, block, 0, st>>>(A, lda, W, ldw, C, ldc, T, N, K, bias, resid, ldr, alpha);
-            else k_dense_rows<WT, ROWS_MAX_T, false><<<grid, block, 0, st>>>(A, lda, W, ldw, C, ldc, T, N, K, bias, resid, ldr, alpha);
+            if (vec) k_dense_rows<WT, ROWS_MAX_T, true><<<grid, block, 0, st>>>(A, lda, W, ldw, C, ldc, T, N, K, bias, resid, ldr, alpha, KS);
+            else k_dense_rows<WT, ROWS_MAX_T, false><<<grid, block, 0, st>>>(A, lda, W, ldw, C, ldc, T, N, K, bias, resid, ldr, alpha, KS);
         }
         return (int) cudaGetLastError();
     }

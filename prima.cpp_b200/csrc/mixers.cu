@@ -144,15 +144,27 @@ __global__ void k_gelu_mul(const float * __restrict__ gu, OT * __restrict__ y, i
     put(y, i, act * u);
 }
 
-__global__ void __launch_bounds__(256) k_argmax_rows(const float * __restrict__ x, int n, int32_t * __restrict__ out) {
-    __shared__ float sv[8];
-    __shared__ int si[8];
+// first index of the row's maximum: one CTA per row, every thread walks its elements in ascending order (16-byte loads when the row allows)
+__global__ void __launch_bounds__(1024) k_argmax_rows(const float * __restrict__ x, int n, int32_t * __restrict__ out) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
     const float * row = x + (int64_t) blockIdx.x * n;
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = row[i];
-        if (v > best) { best = v; bi = i; }
+    if ((n & 3) == 0 && ((uintptr_t) row & 15) == 0) {
+        const float4 * r4 = reinterpret_cast<const float4 *>(row);
+        for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
+            const float4 v = r4[i];
+            if (v.x > best) { best = v.x; bi = 4 * i; }
+            if (v.y > best) { best = v.y; bi = 4 * i + 1; }
+            if (v.z > best) { best = v.z; bi = 4 * i + 2; }
+            if (v.w > best) { best = v.w; bi = 4 * i + 3; }
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float v = row[i];
+            if (v > best) { best = v; bi = i; }
+        }
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
@@ -892,7 +904,7 @@ int launch_gelu_mul(const float * gu, void * y, int otype, int n_tokens, int ff,
 }
 int launch_argmax_rows(const float * logits, int n, int n_rows, int32_t * out, cudaStream_t st) {
     if (n_rows <= 0) return 0;
-    return ck_launch([&] { k_argmax_rows<<<n_rows, 256, 0, st>>>(logits, n, out); });
+    return ck_launch([&] { k_argmax_rows<<<n_rows, n >= 8192 ? 1024 : 256, 0, st>>>(logits, n, out); });
 }
 
 int launch_attn_kv_store(const float * qkvg, const BatchView & b, const AttnParams & a, float * kcache, float * vcache, int64_t slot_stride, cudaStream_t st) {

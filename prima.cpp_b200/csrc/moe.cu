@@ -109,7 +109,7 @@ __device__ __forceinline__ void warp_argmax(const float * v, int n, int lane, fl
 
 // one CTA per token: sigmoid scores, choice with the correction among the experts of the best groups, weights from the plain scores
 template <typename HT>
-__global__ void __launch_bounds__(256) k_moe_route_sigmoid(const HT * __restrict__ h, const float * __restrict__ wr, const float * __restrict__ corr, MoeParams p,
+__global__ void __launch_bounds__(1024) k_moe_route_sigmoid(const HT * __restrict__ h, const float * __restrict__ wr, const float * __restrict__ corr, MoeParams p,
                                                            int width, const float * __restrict__ sgw, int32_t * __restrict__ idx, float * __restrict__ wt,
                                                            float * __restrict__ sg_out) {
     extern __shared__ float sm[];
@@ -304,16 +304,19 @@ int launch_moe_route_sigmoid(const void * h, int htype, const float * wr, const 
         (int64_t) p.keep_groups * (p.experts / p.groups) < p.top)
         return (int) cudaErrorInvalidValue;
     const size_t smem = ((size_t) width + 2 * (size_t) p.experts + 2 * (size_t) p.groups) * sizeof(float);
+    // one warp per router row (the shared gate included) up to 32 warps, so that all rows stream at once
+    const int rows = p.experts + (shared_gate ? 1 : 0);
+    const int threads = rows <= 8 ? 256 : rows >= 32 ? 1024 : 32 * rows;
     if (htype == T_BF16) {
         int rc = raise_smem(k_moe_route_sigmoid<__nv_bfloat16>, smem);
         if (rc) return rc;
         return ck_launch([&] {
-            k_moe_route_sigmoid<__nv_bfloat16><<<n_tokens, 256, smem, st>>>((const __nv_bfloat16 *) h, wr, correction, p, width, shared_gate, idx, wt, sg_out);
+            k_moe_route_sigmoid<__nv_bfloat16><<<n_tokens, threads, smem, st>>>((const __nv_bfloat16 *) h, wr, correction, p, width, shared_gate, idx, wt, sg_out);
         });
     }
     int rc = raise_smem(k_moe_route_sigmoid<float>, smem);
     if (rc) return rc;
-    return ck_launch([&] { k_moe_route_sigmoid<float><<<n_tokens, 256, smem, st>>>((const float *) h, wr, correction, p, width, shared_gate, idx, wt, sg_out); });
+    return ck_launch([&] { k_moe_route_sigmoid<float><<<n_tokens, threads, smem, st>>>((const float *) h, wr, correction, p, width, shared_gate, idx, wt, sg_out); });
 }
 int launch_moe_gateup_rows(const void * h, int type, const void * gateup, const int32_t * idx, const MoeParams & p, int width, void * y, int n_tokens,
                            cudaStream_t st) {
