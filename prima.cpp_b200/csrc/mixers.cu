@@ -344,6 +344,10 @@ __global__ void __launch_bounds__(AQ * 32) k_attn_window_prefill(const AttnIO io
 // dim from transposed shared-memory tiles), the 16 threads of a query row agree on the running max / sum by shuffles, the weights go to
 // shared memory and every thread accumulates queries 4 ty .. +3 x value columns tx + 16 c.  Everything is fp32.
 constexpr int PQ = 64, PK = 64;
+__host__ __device__ inline bool attn_tiled_ps_aliased(int dim) { return dim * (PK + 1) >= PQ * (PK + 1); }
+inline size_t attn_tiled_smem(int dim, int vdim) {
+    return ((size_t) dim * (PQ + 4) + (size_t) dim * (PK + 1) + (size_t) PK * vdim + (attn_tiled_ps_aliased(dim) ? 0 : (size_t) PQ * (PK + 1))) * sizeof(float);
+}
 template <typename OT, int NVC>
 __global__ void __launch_bounds__(256) k_attn_window_prefill_tiled(const AttnIO io, const int32_t * __restrict__ off, AttnParams a,
                                                                    OT * __restrict__ out) {
@@ -359,7 +363,7 @@ __global__ void __launch_bounds__(256) k_attn_window_prefill_tiled(const AttnIO 
     float * Qt = sm;                    // [D][PQS]  transposed: Qt[d][q]
     float * Kt = Qt + D * PQS;          // [D][PKS]  transposed: Kt[d][k]
     float * Vs = Kt + D * PKS;          // [PK][DV]
-    float * Ps = Vs + PK * DV;          // [PQ][PK + 1]
+    float * Ps = attn_tiled_ps_aliased(D) ? Kt : Vs + PK * DV;   // [PQ][PK + 1]; shares the key tile's memory when that is large enough (two CTAs per SM fit then)
     for (int i = tid; i < PQ * D; i += 256) {
         const int q = i / D, d = i - q * D;
         Qt[d * PQS + q] = q0 + q < n ? io.q[(int64_t) (t_begin + q0 + q) * io.ldq + h * D + d] * a.scale : 0.f;
@@ -424,6 +428,7 @@ __global__ void __launch_bounds__(256) k_attn_window_prefill_tiled(const AttnIO 
 #pragma unroll
                     for (int j = 0; j < 4; j++) s[i][j] = fmaf(qq[i], kv[j], s[i][j]);
             }
+            __syncthreads();   // every warp is done with the key tile before the weights overwrite it
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int qi = q0 + ty * 4 + i;
@@ -933,7 +938,7 @@ int launch_attn_qknorm_kv_store(float * qkvg, const BatchView & b, const AttnPar
 
 template <typename OT, int NVC>
 static int attn_prefill_tiled_typed(const AttnIO & io, const BatchView & b, const AttnParams & a, OT * out, cudaStream_t st) {
-    const size_t smem = ((size_t) a.dim * (PQ + 4) + (size_t) a.dim * (PK + 1) + (size_t) PK * a.vdim + (size_t) PQ * (PK + 1)) * sizeof(float);
+    const size_t smem = attn_tiled_smem(a.dim, a.vdim);
     int rc = raise_smem(k_attn_window_prefill_tiled<OT, NVC>, smem);
     if (rc) return rc;
     const dim3 grid((unsigned) ((b.max_n + PQ - 1) / PQ), (unsigned) a.heads, (unsigned) b.n_entries);
@@ -953,7 +958,7 @@ int launch_attn_prefill_io(const AttnIO & io, const BatchView & b, const AttnPar
         (a.shared_dim > 0 && !io.ks))
         return (int) cudaErrorInvalidValue;
     static const bool no_tiled = getenv("PB200_ATTN_ROWWISE") != nullptr;   // A/B: the one-warp-per-query kernel for every length
-    const size_t tiled_smem = ((size_t) a.dim * (PQ + 4) + (size_t) a.dim * (PK + 1) + (size_t) PK * a.vdim + (size_t) PQ * (PK + 1)) * sizeof(float);
+    const size_t tiled_smem = attn_tiled_smem(a.dim, a.vdim);
     if (b.max_n > 16 && !no_tiled && tiled_smem <= 220 * 1024) {   // long entries: 64-query tiles; the same numbers up to fp32 summation order
         const int nvc = (a.vdim + 15) / 16;
         if (nvc <= 16) {
