@@ -1,7 +1,7 @@
 // prima.cpp_b200/csrc/arch.h — the table of model architectures this library runs.  Two families:
 //   ARCH_KQUANT   one fixed transformer graph over k-quant GGUF weights (engine.cu): "llama", "qwen2"
 //   ARCH_LAYERS   the configuration lists the layers, each with a sequence mixer and an optional feed-forward, over dense
-//                 f32 / bf16 weights from a safetensors file (layers.cu): "Vamidra", "Mumizen", "Sapudra"
+//                 f32 / bf16 weights from a safetensors file (layers.cu): "Vamidra", "Mumizen", "Sapudra", "Zevedra"
 // A loader looks the architecture string of its container up here (GGUF: general.architecture; configuration file: "architecture")
 // and takes the family's path; an unknown string is PB200_ENOTSUP.
 #pragma once

@@ -1,9 +1,11 @@
 // prima.cpp_b200/csrc/layers.cu — the engine of the layer-list family (arch.h): a configuration file lists the layers, every layer has
 // a sequence mixer (windowed attention with kept first tokens, a Mamba-2 state-space mixer, linear attention with a fixed decay per
-// head, or softmax attention over a low-rank latent) and an optional feed-forward (tanh-GELU gated; clamped gated, dense or a routed
-// mixture of experts), inside one of two layer frames: norms before and after every sublayer (FRAME_SANDWICH), or a grouped RMS norm
+// head, softmax attention over a low-rank latent, or a dual mixer: an attention branch beside a gated linear recurrence) and an optional
+// feed-forward (tanh-GELU gated; clamped gated, dense or a routed mixture of experts), inside one of these layer frames: norms before and after every sublayer (FRAME_SANDWICH), or a grouped RMS norm
 // before it with token shift and a depth average of all layer results (FRAME_PRENORM), or a layer norm with weight and bias on the
-// sublayer's result only, scaled by one factor, with a learned position table on the embedding (FRAME_POSTNORM).  Weights are dense f32 / bf16 matrices.  It lives behind the same model object and C ABI as the k-quant transformer engine
+// sublayer's result only, scaled by one factor, with a learned position table on the embedding (FRAME_POSTNORM), or an RMS norm with one
+// learned number before every sublayer, sublayer results times one factor, and a repeated block whose passes add the embedding output and
+// a step vector (FRAME_PRERMS).  Weights are dense f32 / bf16 matrices.  It lives behind the same model object and C ABI as the k-quant transformer engine
 // (engine.cu): pb200_model_set_tensor / _synth / _finalize / _free, sequence slots, device arg-max — and steps through the ragged
 // batch step (pb200_batch_step) that the scheduler drives; the single-sequence entry points of the k-quant family answer PB200_ENOTSUP.
 //
@@ -11,8 +13,9 @@
 // times per token and each pass has its own state): attention -> K and V rows (positions below keep_first at their own row, later ones
 // in a ring as long as the window), Mamba-2 -> the last taps-1 convolution inputs and the fp32 state [heads][state][vdim], decay
 // attention -> the fp32 state [heads][dim][vdim], latent attention -> one row [latent | rotated key part] per position (a layer that
-// reads another layer's latent has none of its own), token shift -> the normed input of the last token.  A slot's arena is zeroed when
-// it is handed out, so a reused slot starts like a new one.
+// reads another layer's latent has none of its own), token shift -> the normed input of the last token, dual mixer -> K and V rows, the
+// last taps-1 convolution inputs of both branches and the recurrence's fp32 state.  A slot's arena is zeroed when it is handed out, so a
+// reused slot starts like a new one; the token before a sequence's next one (bigram embedding) is kept per slot on the host.
 //
 // Precision: the residual stream, norms, attention scores / weights, recurrent state and everything that feeds the recurrence are
 // fp32 in both compute types; with T_BF16 only the two operands of a dense product are bf16 (fp32 accumulation).
@@ -47,10 +50,12 @@ extern std::atomic<uint64_t> g_launches;
 
 namespace pb {
 
-enum : int { MIX_ATTENTION = 0, MIX_MAMBA2 = 1, MIX_DECAY = 2, MIX_LATENT = 3 };
+enum : int { MIX_ATTENTION = 0, MIX_MAMBA2 = 1, MIX_DECAY = 2, MIX_LATENT = 3, MIX_DUAL = 4 };
 enum : int { FF_GELU = 0, FF_CLAMPED = 1, FF_MOE = 2, FF_RELU2 = 3 };   // FF_MOE: the expert form is MoeParams::act
-enum : int { FRAME_SANDWICH = 0, FRAME_PRENORM = 1, FRAME_POSTNORM = 2 };
-enum : int { ROUTE_SOFTMAX_TOP = 0, ROUTE_SIGMOID_GROUPS = 1 };
+enum : int { FRAME_SANDWICH = 0, FRAME_PRENORM = 1, FRAME_POSTNORM = 2, FRAME_PRERMS = 3 };
+enum : int { ROUTE_SOFTMAX_TOP = 0, ROUTE_SIGMOID_GROUPS = 1, ROUTE_SIGMOID_PLAIN = 2 };
+enum : int { REC_DELTA = 0, REC_HGRN2 = 1 };                 // recurrent branch of a dual mixer
+enum : int { JOIN_SCALED_SUM = 0, JOIN_NORMED_MEAN = 1 };    // a * left + b * right through one output product, or the mean of the two normed results
 
 struct DenseW {           // row-major [N][K] in the model's compute type
     void * data = nullptr;
@@ -62,6 +67,21 @@ struct VecF {             // small fp32 parameter (norm weights, convolution tap
     int64_t n = 0;
     bool filled = false;
     std::vector<float> preset;   // non-empty: values the configuration fixes (decays, rotation frequencies); no checkpoint tensor fills it
+    int n_parts = 0;             // > 0: several checkpoint tensors fill it, one flag each
+    std::vector<uint8_t> parts;
+};
+
+// dual mixer: an attention branch (LLayer::att) and a gated linear recurrence side by side over the same input, ONE fused projection
+struct DualMix {
+    int rec = REC_DELTA, join = JOIN_SCALED_SUM;
+    float left_scale = 1.f, right_scale = 1.f;
+    int taps_l = 0, taps_r = 0, taps = 0;   // short convolution of the two branches (0: none); taps = the longer one, the shorter is padded with zero taps
+    int qk_norm = QKN_NONE, rot_dims = 0, rot_layout = ROT_INTERLEAVED, v_rot = 0;
+    int gate_mode = 1;                      // 1: a gate logit per head, 2: per output element
+    GatedLinParams rp;
+    // columns of the fused projection: left q | k | v, right q | k (HGRN2: forget logits) | v, then gates and per-head numbers; the first
+    // conv_ch columns pass the convolution (the first conv_l of them without activation, the rest with SiLU)
+    int c_q = 0, c_k = 0, c_v = 0, c_rq = 0, c_rk = 0, c_rv = 0, c_g = 0, c_rb = 0, c_ra = 0, c_rg = 0, cols = 0, conv_ch = 0, conv_l = 0;
 };
 
 struct LLayer {
@@ -103,6 +123,10 @@ struct LLayer {
     // mixture of experts: form of the router; the shared expert's per-token gate vector [width] (ROUTE_SIGMOID_GROUPS)
     int route = ROUTE_SOFTMAX_TOP;
     VecF shared_gate;
+    // dual mixer (qkvg: the fused projection of both branches; out: the output product over [left | right], or the left one; out_r: the right one)
+    DualMix dual;
+    DenseW out_r;
+    VecF dconv_w, vrot_freq, f_bias, f_lower, join_wl, join_wr;   // rot_freq, q_norm, k_norm, A_log, dt_bias, onorm are shared with the other mixers
 };
 
 struct LRun {
@@ -114,11 +138,14 @@ struct LRun {
 
 // where a checkpoint tensor goes
 struct TensorPlace {
-    DenseW * mat = nullptr;   // rows [row0, row0 + rows) of a matrix with `cols` columns ...
-    int64_t row0 = 0, rows = 0, cols = 0;
-    int part = 0;             // index into mat->filled
-    VecF * vec = nullptr;     // ... or a whole fp32 vector of n elements
+    DenseW * mat = nullptr;   // rows [row0, row0 + rows) of a matrix, columns [col0, col0 + cols) (col0 == 0 and cols == K: whole rows) ...
+    int64_t row0 = 0, rows = 0, cols = 0, col0 = 0;
+    int part = 0;             // index into mat->filled / vec->parts
+    VecF * vec = nullptr;     // ... or a whole fp32 vector of n elements ...
     int64_t n = 0;
+    // ... or (vrows > 0) a tensor [vrows][vcols] (n = vrows * vcols) placed at element v0 + r * vld + c, `repeat` copies vrep elements apart:
+    // a block of a vector several tensors fill, a short convolution right-aligned in longer taps, a weight all heads share, one number for all
+    int64_t v0 = 0, vrows = 0, vcols = 0, vld = 0, repeat = 1, vrep = 0;
 };
 
 struct LayerList {
@@ -140,7 +167,12 @@ struct LayerList {
     DenseW pos_table;         // learned position vectors [max_pos][width], added to the embedding
     int max_pos = 0;
     VecF final_norm_bias;
-    float resid_mult = 1.f;   // factor on every normed sublayer result
+    float resid_mult = 1.f;   // factor on every normed sublayer result (FRAME_PRERMS: on every sublayer result)
+    // FRAME_PRERMS: embedding factor, hashed bigram table [buckets + 1][width] (buckets == 0: none), the token before each slot's next one
+    float embed_scale = 1.f;
+    BigramParams bigram;
+    DenseW bigram_table;
+    std::vector<int32_t> seq_prev;
     float logit_softcap = 0.f;   // > 0: logits <- cap * tanh(logits / cap)
     // state manager
     int n_ctx = 0, n_seq = 0;
@@ -636,12 +668,289 @@ static bool sapudra_resolve(LayerList & ll, const std::string & name, TensorPlac
     return false;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Zevedra: configuration keys and tensor names.  The stream starts as embed[token] * scale + a hashed bigram row; every layer is
+// x <- x + m mixer(norm x), x <- x + m ff(norm x) with an RMS norm of one learned number; a repeated block whose passes add the embedding
+// output and a step vector.  Mixers are dual: "parallel" = windowed softmax attention (short convolution on q, k, v, interleaved partial
+// rotation, unit RMS per head after it, values turned by their position, a gate per head) beside the gated delta rule, joined as
+// a * left + b * right; "parallel_2" = causal attention with a sink (RMS norm with weight over the whole q / k projection before a
+// rotate-half partial rotation, a gate per element) beside HGRN2, joined as the mean of the two normed results.  Feed-forward: SiLU-gated
+// experts, sigmoid router, the plain scores of the chosen experts multiply their input.
+static void plain_rotary_table(double base, int dims, std::vector<float> & freq) {
+    freq.assign((size_t) std::max(dims / 2, 1), 0.f);
+    for (int i = 0; i < dims / 2; i++) freq[(size_t) i] = (float) std::pow(base, -2.0 * i / dims);
+}
+static int zevedra_attention(const Json & jl, AttnParams & a, DualMix & d, LLayer & L, std::string & err) {
+    a.heads = (int) jl.integer("heads", 0);
+    a.kv_heads = (int) jl.integer("kv_heads", a.heads);
+    a.dim = (int) jl.integer("dim", 0);
+    a.vdim = (int) jl.integer("vdim", a.dim);
+    a.scale = (float) jl.number("scale", a.dim > 0 ? 1.0 / std::sqrt((double) a.dim) : 1.0);
+    a.softcap = 0.f;
+    a.gated = 0;
+    a.window = 0;
+    a.keep_first = 0;
+    if (const Json * mk = jl.get("mask"))
+        if (mk->kind == Json::OBJ) a.window = (int) std::min<long long>(mk->integer("size", 0), 1 << 30);
+    if (a.heads <= 0 || a.kv_heads <= 0 || a.heads % a.kv_heads || a.dim <= 0 || a.vdim <= 0 || a.vdim > 512) { err = "attention sizes"; return PB200_EINVAL; }
+    double base = 10000.0;
+    d.rot_dims = 0;
+    const Json * rot = jl.get("rot");
+    if (rot && rot->kind == Json::OBJ) {
+        base = rot->number("base", 10000.0);
+        d.rot_dims = (int) rot->integer("dims", a.dim);
+        if (d.rot_dims < 0 || d.rot_dims > a.dim || d.rot_dims % 2 || !(base > 0.0)) { err = "rotated dimensions"; return PB200_EINVAL; }
+    }
+    plain_rotary_table(base, d.rot_dims, L.rot_freq.preset);
+    if (d.v_rot) {
+        if (a.vdim % 2) { err = "rotated values need an even value size"; return PB200_EINVAL; }
+        plain_rotary_table(base, a.vdim, L.vrot_freq.preset);
+    }
+    d.taps_l = (int) jl.integer("conv", 0);
+    if (d.taps_l < 0 || d.taps_l > 64) { err = "convolution taps"; return PB200_EINVAL; }
+    return 0;
+}
+
+static int zevedra_configure(const Json & cfg, LayerList & ll, std::string & err) {
+    ll.frame = FRAME_PRERMS;
+    ll.width = (int) cfg.integer("width", 0);
+    ll.vocab = (int) cfg.integer("vocab", 0);
+    ll.resid_mult = (float) cfg.number("residual_mult", 1.0);
+    ll.logit_scale = 1.f;
+    if (const Json * nrm = cfg.get("norm")) ll.eps = (float) nrm->number("eps", 1e-6);
+    if (const Json * em = cfg.get("embedding")) {
+        if (em->kind == Json::OBJ) {
+            ll.embed_scale = (float) em->number("scale", 1.0);
+            const Json * bg = em->get("bigram");
+            if (bg && bg->kind == Json::OBJ) {
+                ll.bigram.buckets = bg->integer("buckets", 0);
+                ll.bigram.mul_prev = bg->integer("mul_prev", 0);
+                ll.bigram.mul_cur = bg->integer("mul_cur", 0);
+                if (ll.bigram.buckets <= 0 || ll.bigram.buckets > (1ll << 30) || ll.bigram.mul_prev < 0 || ll.bigram.mul_cur < 0 ||
+                    ll.bigram.mul_prev > (1ll << 30) || ll.bigram.mul_cur > (1ll << 30)) { err = "bigram sizes"; return PB200_EINVAL; }
+            }
+        }
+    }
+    const Json * layers = cfg.get("layers");
+    if (ll.width <= 0 || ll.vocab <= 0 || !layers || layers->kind != Json::ARR || layers->arr.empty()) { err = "width, vocab and layers are required"; return PB200_EINVAL; }
+    for (const Json & jl : layers->arr) {
+        LLayer L;
+        L.kind = MIX_DUAL;
+        DualMix & d = L.dual;
+        const std::string type = jl.string("type");
+        const Json * mx = jl.get("mixer");
+        const Json * jle = mx && mx->kind == Json::OBJ ? mx->get("left") : nullptr, * jr = mx && mx->kind == Json::OBJ ? mx->get("right") : nullptr;
+        if (!jle || jle->kind != Json::OBJ || !jr || jr->kind != Json::OBJ) { err = "a dual mixer needs left and right"; return PB200_EINVAL; }
+        GatedLinParams & rp = d.rp;
+        rp.heads = (int) jr->integer("heads", 0);
+        rp.qk_heads = (int) jr->integer("kv_heads", rp.heads);
+        rp.dim = (int) jr->integer("dim", 0);
+        rp.vdim = (int) jr->integer("vdim", rp.dim);
+        if (rp.heads <= 0 || rp.qk_heads <= 0 || rp.heads % rp.qk_heads || rp.dim <= 0 || rp.vdim <= 0 || rp.dim > 512) { err = "recurrence sizes"; return PB200_EINVAL; }
+        AttnParams & a = L.att;
+        if (type == "parallel") {
+            d.rec = REC_DELTA; d.join = JOIN_SCALED_SUM;
+            d.qk_norm = QKN_HEAD_UNIT; d.rot_layout = ROT_INTERLEAVED; d.v_rot = 1; d.gate_mode = 1;
+            a.sink = 0;
+            rp.delta = 1; rp.decay_per_channel = 0; rp.tied_key = 0;
+            d.left_scale = (float) mx->number("left_scale", 1.0);
+            d.right_scale = (float) mx->number("right_scale", 1.0);
+            d.taps_r = (int) jr->integer("conv", 0);
+        } else if (type == "parallel_2") {
+            d.rec = REC_HGRN2; d.join = JOIN_NORMED_MEAN;
+            d.qk_norm = QKN_WHOLE_WEIGHT; d.rot_layout = ROT_HALVES; d.v_rot = 0; d.gate_mode = 2;
+            rp.delta = 0; rp.decay_per_channel = 1; rp.tied_key = 1;
+            rp.qk_heads = rp.heads;
+            d.left_scale = d.right_scale = 0.5f;
+        } else {
+            err = "unknown layer type '" + type + "'";
+            return PB200_ENOTSUP;
+        }
+        int rc = zevedra_attention(*jle, a, d, L, err);
+        if (rc) return rc;
+        if (type == "parallel") {
+            // every delta-rule input passes convolution + SiLU; a branch without taps is not part of the design
+            if (d.taps_l < 1 || d.taps_r < 1 || d.taps_r > 64) { err = "parallel: convolution taps of both branches"; return PB200_EINVAL; }
+            d.taps = std::max(d.taps_l, d.taps_r);
+        } else {
+            a.sink = 1;
+            d.taps_l = d.taps_r = d.taps = 0;
+        }
+        // columns of the fused projection
+        const int QD = a.heads * a.dim, KD = a.kv_heads * a.dim, VD = a.kv_heads * a.vdim, OD = a.heads * a.vdim;
+        const int RQ = rp.qk_heads * rp.dim, RV = rp.heads * rp.vdim;
+        int c = 0;
+        d.c_q = c; c += QD;
+        d.c_k = c; c += KD;
+        d.c_v = c; c += VD;
+        d.conv_l = c;
+        if (d.rec == REC_DELTA) {
+            d.c_rq = c; c += RQ;
+            d.c_rk = c; c += RQ;
+            d.c_rv = c; c += RV;
+            d.conv_ch = c;
+            d.c_g = c; c += a.heads;
+            d.c_rb = c; c += rp.heads;
+            d.c_ra = c; c += rp.heads;
+            d.c_rg = c; c += RV;
+        } else {
+            d.conv_ch = 0;
+            d.c_g = c; c += OD;
+            d.c_rq = c; c += RQ;
+            d.c_rk = c; c += RQ;     // forget-gate logits
+            d.c_rv = c; c += RV;
+        }
+        d.cols = c;
+        L.dconv_w.n_parts = d.taps > 0 ? 6 : 0;
+        L.ff = 0;
+        const Json * mlp = jl.get("mlp");
+        if (mlp && mlp->kind == Json::OBJ) {
+            const std::string kind = mlp->string("kind", "moe");
+            if (kind != "moe") { err = "unknown feed-forward kind '" + kind + "'"; return PB200_ENOTSUP; }
+            L.ff_kind = FF_MOE;
+            L.route = ROUTE_SIGMOID_PLAIN;
+            MoeParams & p = L.moe;
+            p.act = 2;
+            p.weight_on_input = 1;
+            p.norm_weights = 0;
+            p.route_scale = 1.f;
+            p.groups = p.keep_groups = 1;
+            const Json * ex = mlp->get("expert"), * ro = mlp->get("router");
+            if (!ex || ex->kind != Json::OBJ || !ro || ro->kind != Json::OBJ) { err = "moe needs expert and router"; return PB200_EINVAL; }
+            p.ff = (int) ex->integer("ff", 0);
+            L.ff = p.ff;
+            p.experts = (int) ro->integer("experts", 0);
+            p.top = (int) ro->integer("top", 0);
+            if (p.ff <= 0 || p.experts <= 0 || p.top <= 0 || p.top > p.experts || p.top > 32 || p.experts > 4096) { err = "router sizes"; return PB200_EINVAL; }
+        }
+        ll.layers.push_back(std::move(L));
+    }
+    const int nl = (int) ll.layers.size();
+    ll.loop_times = 0;
+    if (const Json * lp = cfg.get("loop")) {
+        if (lp->kind == Json::OBJ) {
+            ll.loop_start = (int) lp->integer("start", 0);
+            ll.loop_stop = (int) lp->integer("stop", 0);
+            ll.loop_times = (int) lp->integer("times", 1);
+            if (ll.loop_start < 0 || ll.loop_stop > nl || ll.loop_start >= ll.loop_stop || ll.loop_times < 1) { err = "loop range"; return PB200_EINVAL; }
+        }
+    }
+    for (int i = 0; i < nl;) {
+        if (ll.loop_times > 0 && i == ll.loop_start) {
+            for (int t = 0; t < ll.loop_times; t++)
+                for (int k = ll.loop_start; k < ll.loop_stop; k++) {
+                    LRun r;
+                    r.layer = k;
+                    r.pass = k == ll.loop_start ? t : -1;
+                    ll.runs.push_back(r);
+                }
+            i = ll.loop_stop;
+        } else {
+            LRun r;
+            r.layer = i++;
+            ll.runs.push_back(r);
+        }
+    }
+    return 0;
+}
+
+static bool zevedra_resolve(LayerList & ll, const std::string & name, TensorPlace & o) {
+    const int64_t W = ll.width;
+    auto mat = [&](DenseW & m, int64_t row0, int64_t rows, int64_t cols, int part) { o.mat = &m; o.row0 = row0; o.rows = rows; o.cols = cols; o.part = part; return true; };
+    auto matc = [&](DenseW & m, int64_t col0, int64_t rows, int64_t cols, int part) { o.mat = &m; o.row0 = 0; o.col0 = col0; o.rows = rows; o.cols = cols; o.part = part; return true; };
+    auto vec = [&](VecF & v, int64_t n) { o.vec = &v; o.n = n; return true; };
+    // a tensor of n elements copied `times` times back to back: one number for a whole row, a weight that all heads share
+    auto tiled = [&](VecF & v, int64_t n, int64_t times) { o.vec = &v; o.n = n; o.vrows = 1; o.vcols = n; o.vld = n; o.repeat = times; o.vrep = n; return true; };
+    if (name == "embed") return mat(ll.embed, 0, ll.vocab, W, 0);
+    if (name == "bigram") return ll.bigram.buckets > 0 && mat(ll.bigram_table, 0, ll.bigram.buckets + 1, W, 0);
+    if (name == "head") return mat(ll.head, 0, ll.vocab, W, 0);
+    if (name == "final.norm") return tiled(ll.final_norm, 1, W);
+    if (name == "loop.step") return ll.loop_times > 0 && vec(ll.loop_step, (int64_t) ll.loop_times * W);
+    int il = -1, used = 0;
+    if (sscanf(name.c_str(), "l%d.%n", &il, &used) != 1 || used <= 0 || il < 0 || il >= (int) ll.layers.size()) return false;
+    LLayer & L = ll.layers[(size_t) il];
+    const std::string w = name.substr((size_t) used);
+    if (w == "norm1") return tiled(L.norm1, 1, W);
+    if (w.compare(0, 4, "mlp.") == 0 || w == "norm2") {
+        if (L.ff <= 0) return false;
+        if (w == "norm2") return tiled(L.norm2, 1, W);
+        const std::string f = w.substr(4);
+        if (f == "router") { o.vec = &L.router; o.n = (int64_t) L.moe.experts * W; return true; }
+        int e = -1, u2 = 0;
+        if (sscanf(f.c_str(), "e%d.%n", &e, &u2) == 1 && u2 > 0 && e >= 0 && e < L.moe.experts) {
+            const std::string leaf = f.substr((size_t) u2);
+            const int64_t ff = L.moe.ff;
+            if (leaf == "gate") return mat(L.e_gateup, (int64_t) e * 2 * ff, ff, W, 2 * e);
+            if (leaf == "up") return mat(L.e_gateup, (int64_t) e * 2 * ff + ff, ff, W, 2 * e + 1);
+            if (leaf == "down") return mat(L.e_down, (int64_t) e * W, W, ff, e);
+        }
+        return false;
+    }
+    const DualMix & d = L.dual;
+    const AttnParams & a = L.att;
+    const GatedLinParams & rp = d.rp;
+    const int64_t QD = (int64_t) a.heads * a.dim, KD = (int64_t) a.kv_heads * a.dim, VD = (int64_t) a.kv_heads * a.vdim, OD = (int64_t) a.heads * a.vdim;
+    const int64_t RQ = (int64_t) rp.qk_heads * rp.dim, RV = (int64_t) rp.heads * rp.vdim;
+    // a short convolution [channels][its taps] right-aligned in the layer's common tap count (the taps in front stay zero)
+    auto conv = [&](int col0, int64_t ch, int taps, int part) {
+        o.vec = &L.dconv_w; o.n = ch * taps; o.part = part;
+        o.v0 = (int64_t) col0 * d.taps + (d.taps - taps); o.vrows = ch; o.vcols = taps; o.vld = d.taps; o.repeat = 1; o.vrep = 0;
+        return true;
+    };
+    const bool sum = d.join == JOIN_SCALED_SUM;
+    if (w.compare(0, 9, "mix.left.") == 0) {
+        const std::string f = w.substr(9);
+        if (f == "q") return mat(L.qkvg, d.c_q, QD, W, 0);
+        if (f == "k") return mat(L.qkvg, d.c_k, KD, W, 1);
+        if (f == "v") return mat(L.qkvg, d.c_v, VD, W, 2);
+        if (f == "g") return mat(L.qkvg, d.c_g, d.gate_mode == 1 ? a.heads : OD, W, 3);
+        if (f == "o") return sum ? matc(L.out, 0, W, OD, 0) : mat(L.out, 0, W, OD, 0);
+        if (d.taps > 0) {
+            if (f == "q.conv") return conv(d.c_q, QD, d.taps_l, 0);
+            if (f == "k.conv") return conv(d.c_k, KD, d.taps_l, 1);
+            if (f == "v.conv") return conv(d.c_v, VD, d.taps_l, 2);
+        }
+        if (d.qk_norm == QKN_WHOLE_WEIGHT) {
+            if (f == "q.norm") return vec(L.q_norm, QD);
+            if (f == "k.norm") return vec(L.k_norm, KD);
+        }
+        if (!sum && f == "out") return vec(L.join_wl, W);
+        return false;
+    }
+    if (w.compare(0, 10, "mix.right.") == 0) {
+        const std::string f = w.substr(10);
+        if (f == "q") return mat(L.qkvg, d.c_rq, RQ, W, 4);
+        if (f == "v") return mat(L.qkvg, d.c_rv, RV, W, 6);
+        if (f == "norm") return tiled(L.onorm, rp.vdim, rp.heads);
+        if (f == "o") return sum ? matc(L.out, OD, W, RV, 1) : mat(L.out_r, 0, W, RV, 0);
+        if (d.rec == REC_DELTA) {
+            if (f == "k") return mat(L.qkvg, d.c_rk, RQ, W, 5);
+            if (f == "b") return mat(L.qkvg, d.c_rb, rp.heads, W, 7);
+            if (f == "a") return mat(L.qkvg, d.c_ra, rp.heads, W, 8);
+            if (f == "g") return mat(L.qkvg, d.c_rg, RV, W, 9);
+            if (f == "A_log") return vec(L.A_log, rp.heads);
+            if (f == "dt_bias") return vec(L.dt_bias, rp.heads);
+            if (f == "q.conv") return conv(d.c_rq, RQ, d.taps_r, 3);
+            if (f == "k.conv") return conv(d.c_rk, RQ, d.taps_r, 4);
+            if (f == "v.conv") return conv(d.c_rv, RV, d.taps_r, 5);
+        } else {
+            if (f == "f") return mat(L.qkvg, d.c_rk, RQ, W, 5);
+            if (f == "f.b") return vec(L.f_bias, RQ);
+            if (f == "lower") return vec(L.f_lower, RQ);
+            if (!sum && f == "out") return vec(L.join_wr, W);
+        }
+        return false;
+    }
+    return false;
+}
+
 static const ArchEntry g_archs[] = {
     {"llama", ARCH_KQUANT, 0, nullptr, nullptr},
     {"qwen2", ARCH_KQUANT, 2, nullptr, nullptr},
     {"Vamidra", ARCH_LAYERS, 0, vamidra_configure, vamidra_resolve},
     {"Mumizen", ARCH_LAYERS, 0, mumizen_configure, mumizen_resolve},
     {"Sapudra", ARCH_LAYERS, 0, sapudra_configure, sapudra_resolve},
+    {"Zevedra", ARCH_LAYERS, 0, zevedra_configure, zevedra_resolve},
 };
 int arch_count() { return (int) (sizeof(g_archs) / sizeof(g_archs[0])); }
 const ArchEntry * arch_at(int i) { return (i >= 0 && i < arch_count()) ? &g_archs[i] : nullptr; }
@@ -663,13 +972,17 @@ static void for_each_param(LayerList & ll, FM && fm, FV && fv) {
     fm(ll.head, (int64_t) ll.vocab, W, 1);
     fv(ll.final_norm, W, 0);
     if (ll.frame == FRAME_POSTNORM) { fm(ll.pos_table, (int64_t) ll.max_pos, W, 1); fv(ll.final_norm_bias, W, 1); }
-    if (ll.loop_times > 0) { fm(ll.loop_in, W, 2 * W, 1); fv(ll.loop_step, (int64_t) ll.loop_times * W, 1); }
+    if (ll.frame == FRAME_PRERMS && ll.bigram.buckets > 0) fm(ll.bigram_table, ll.bigram.buckets + 1, W, 1);
+    if (ll.loop_times > 0) {
+        if (ll.frame != FRAME_PRERMS) fm(ll.loop_in, W, 2 * W, 1);
+        fv(ll.loop_step, (int64_t) ll.loop_times * W, 1);
+    }
     int il = 0;
     for (LLayer & L : ll.layers) {
         fv(L.norm1, W, 0);
         if (ll.frame == FRAME_SANDWICH) fv(L.norm1b, W, 0);
         else if (ll.frame == FRAME_POSTNORM) fv(L.norm1_bias, W, 1);
-        else { fv(L.shift, W, 5); fv(L.dwa, il + 2, 6); }
+        else if (ll.frame == FRAME_PRENORM) { fv(L.shift, W, 5); fv(L.dwa, il + 2, 6); }
         il++;
         if (L.kind == MIX_ATTENTION) {
             fm(L.qkvg, attn_qkvg_cols(L.att), W, L.att.gated ? 4 : 3);
@@ -687,6 +1000,24 @@ static void for_each_param(LayerList & ll, FM && fm, FV && fv) {
             fm(L.out, W, VD, 1);
             fv(L.decay, L.dec.heads, 0);
             if (L.dec_norm_weight) fv(L.onorm, VD, 0);
+        } else if (L.kind == MIX_DUAL) {
+            const DualMix & d = L.dual;
+            const AttnParams & a = L.att;
+            const int64_t OD = (int64_t) a.heads * a.vdim, RQ = (int64_t) d.rp.qk_heads * d.rp.dim, RV = (int64_t) d.rp.heads * d.rp.vdim;
+            fm(L.qkvg, d.cols, W, d.rec == REC_DELTA ? 10 : 7);
+            fv(L.rot_freq, (int64_t) L.rot_freq.preset.size(), 0);
+            if (d.v_rot) fv(L.vrot_freq, (int64_t) L.vrot_freq.preset.size(), 0);
+            if (d.taps > 0) fv(L.dconv_w, (int64_t) d.conv_ch * d.taps, 2);
+            if (d.qk_norm == QKN_WHOLE_WEIGHT) { fv(L.q_norm, (int64_t) a.heads * a.dim, 0); fv(L.k_norm, (int64_t) a.kv_heads * a.dim, 0); }
+            fv(L.onorm, RV, 0);
+            if (d.rec == REC_DELTA) { fv(L.A_log, d.rp.heads, 4); fv(L.dt_bias, d.rp.heads, 3); }
+            else { fv(L.f_bias, RQ, 1); fv(L.f_lower, RQ, 5); }
+            if (d.join == JOIN_SCALED_SUM) {
+                fm(L.out, W, OD + RV, 2);
+            } else {
+                fm(L.out, W, OD, 1); fm(L.out_r, W, RV, 1);
+                fv(L.join_wl, W, 0); fv(L.join_wr, W, 0);
+            }
         } else {
             const LatentParams & a = L.lat;
             fm(L.lproj, latent_proj_cols(a), W, a.own_kv ? 3 : 2);
@@ -703,10 +1034,11 @@ static void for_each_param(LayerList & ll, FM && fm, FV && fv) {
             if (ll.frame == FRAME_SANDWICH) fv(L.norm2b, W, 0);
             if (ll.frame == FRAME_POSTNORM) fv(L.norm2_bias, W, 1);
             if (L.ff_kind == FF_MOE) {
-                const int gated = L.moe.act == 0 ? 2 : 1;   // rows per expert: gate | up, or up only
+                const int gated = L.moe.act == 1 ? 1 : 2;   // rows per expert: up only, or gate | up
                 fm(L.e_gateup, (int64_t) L.moe.experts * moe_up_rows(L.moe), W, gated * L.moe.experts);
                 fm(L.e_down, (int64_t) L.moe.experts * W, L.moe.ff, L.moe.experts);
-                fv(L.router, (int64_t) L.moe.experts * W, 7); fv(L.router_b, L.moe.experts, 1);
+                fv(L.router, (int64_t) L.moe.experts * W, 7);
+                if (L.route != ROUTE_SIGMOID_PLAIN) fv(L.router_b, L.moe.experts, 1);
                 if (L.shared_ff > 0) {
                     fm(L.s_gateup, gated * (int64_t) L.shared_ff, W, gated); fm(L.s_down, W, L.shared_ff, 1);
                     if (L.route == ROUTE_SIGMOID_GROUPS) fv(L.shared_gate, W, 7);
@@ -738,7 +1070,9 @@ static int ll_alloc_params(pb200_model * m) {
         [&](VecF & v, int64_t n, int) {
             if (rc) return;
             v.n = n; v.filled = false;
+            v.parts.assign((size_t) std::max(v.n_parts, 0), 0);
             rc = m->alloc((void **) &v.data, (size_t) n * 4);
+            if (!rc) rc = (int) cudaMemset(v.data, 0, (size_t) n * 4);   // entries no tensor fills (padding taps) are zero
             bytes += n * 4;
             if (!rc && !v.preset.empty()) {   // fixed by the configuration
                 rc = (int) cudaMemcpy(v.data, v.preset.data(), (size_t) n * 4, cudaMemcpyHostToDevice);
@@ -787,9 +1121,21 @@ int ll_set_tensor(pb200_model * m, const char * name, int type, const void * hos
         src = conv.data();
     }
     if (pl.mat) {
-        if (pl.cols != pl.mat->K || pl.row0 + pl.rows > pl.mat->N) return PB200_EINVAL;
-        CK(cudaMemcpy((uint8_t *) pl.mat->data + (size_t) pl.row0 * pl.cols * esize(dtype), src, (size_t) count * esize(dtype), cudaMemcpyHostToDevice));
+        const size_t es = esize(dtype);
+        if (pl.col0 < 0 || pl.col0 + pl.cols > pl.mat->K || pl.row0 + pl.rows > pl.mat->N || (size_t) pl.part >= pl.mat->filled.size()) return PB200_EINVAL;
+        CK(cudaMemcpy2D((uint8_t *) pl.mat->data + ((size_t) pl.row0 * pl.mat->K + (size_t) pl.col0) * es, (size_t) pl.mat->K * es, src, (size_t) pl.cols * es,
+                        (size_t) pl.cols * es, (size_t) pl.rows, cudaMemcpyHostToDevice));
         pl.mat->filled[(size_t) pl.part] = 1;
+    } else if (pl.vrows > 0) {
+        if (pl.vrows * pl.vcols != pl.n || pl.vcols > pl.vld || pl.repeat < 1) return PB200_EINVAL;
+        for (int64_t r = 0; r < pl.repeat; r++) {
+            const int64_t first = pl.v0 + r * pl.vrep;
+            if (first < 0 || first + (pl.vrows - 1) * pl.vld + pl.vcols > pl.vec->n) return PB200_EINVAL;
+            CK(cudaMemcpy2D(pl.vec->data + first, (size_t) pl.vld * 4, src, (size_t) pl.vcols * 4, (size_t) pl.vcols * 4, (size_t) pl.vrows, cudaMemcpyHostToDevice));
+        }
+        if (pl.vec->parts.empty()) pl.vec->filled = true;
+        else if ((size_t) pl.part < pl.vec->parts.size()) pl.vec->parts[(size_t) pl.part] = 1;
+        else return PB200_EINVAL;
     } else {
         if (pl.n != pl.vec->n) return PB200_EINVAL;
         CK(cudaMemcpy(pl.vec->data, src, (size_t) count * 4, cudaMemcpyHostToDevice));
@@ -840,6 +1186,7 @@ int ll_synth(pb200_model * m, uint64_t seed) {
             k_fill_uniform<float><<<(unsigned) ((n + 255) / 256), 256, 0, m->stream>>>(v.data, n, base, hr, ++sd);
             rc = (int) cudaGetLastError();
             v.filled = true;
+            std::fill(v.parts.begin(), v.parts.end(), 1);
         });
     if (rc) return rc;
     return (int) cudaStreamSynchronize(m->stream);
@@ -852,7 +1199,10 @@ int ll_finalize(pb200_model * m) {
     bool complete = true;
     for_each_param(
         ll, [&](DenseW & d, int64_t, int64_t, int) { for (uint8_t f : d.filled) complete = complete && f; },
-        [&](VecF & v, int64_t, int) { complete = complete && v.filled; });
+        [&](VecF & v, int64_t, int) {
+            if (v.parts.empty()) complete = complete && v.filled;
+            else for (uint8_t f : v.parts) complete = complete && f;
+        });
     if (!complete) return PB200_ESTATE;
     // state arena layout of one slot
     int64_t off = 0;
@@ -868,10 +1218,17 @@ int ll_finalize(pb200_model * m) {
             ll.ctx_limited = true;
             if (L.lat.own_kv) off += (int64_t) ll.n_ctx * latent_row(L.lat);
             else r.state_off = ll.runs[(size_t) L.kv_from].state_off;   // FRAME_PRENORM: run i is layer i
-        } else if (L.kind == MIX_ATTENTION) {
+        } else if (L.kind == MIX_ATTENTION || L.kind == MIX_DUAL) {
             L.att.cache_rows = attn_cache_rows(L.att.window, L.att.keep_first, ll.n_ctx);
             if (L.att.cache_rows >= ll.n_ctx) ll.ctx_limited = true;
             off += (int64_t) L.att.cache_rows * L.att.kv_heads * (L.att.dim + L.att.vdim);
+            if (L.kind == MIX_DUAL) {   // then the convolution's last inputs and the recurrence's state
+                const DualMix & d = L.dual;
+                off = (off + 3) / 4 * 4;
+                off += (int64_t) std::max(d.taps - 1, 0) * d.conv_ch;
+                off = (off + 3) / 4 * 4;
+                off += (int64_t) d.rp.heads * d.rp.dim * d.rp.vdim;
+            }
         } else {
             off += (int64_t) (L.ssm.conv - 1) * mamba2_conv_channels(L.ssm) + (int64_t) L.ssm.heads * L.ssm.state * L.ssm.vdim;
         }
@@ -885,6 +1242,7 @@ int ll_finalize(pb200_model * m) {
     CK(m->alloc((void **) &ll.state, (size_t) ll.slot_floats * 4 * (size_t) ll.n_seq));
     CK(cudaMemset(ll.state, 0, (size_t) ll.slot_floats * 4 * (size_t) ll.n_seq));
     ll.seq_len.assign((size_t) ll.n_seq, -1);
+    ll.seq_prev.assign((size_t) ll.n_seq, -1);
     m->n_seq = ll.n_seq;
     m->weight_bytes = ll.weight_bytes;
     m->finalized = true;
@@ -919,6 +1277,7 @@ int ll_seq_alloc(pb200_model * m) {
             // a slot that is handed out again starts from the empty state: zero convolution inputs, zero recurrent state, no cached keys
             if (cudaMemsetAsync(ll.state + (int64_t) s * ll.slot_floats, 0, (size_t) ll.slot_floats * 4, m->stream) != cudaSuccess) return PB200_ENOMEM;
             ll.seq_len[(size_t) s] = 0;
+            ll.seq_prev[(size_t) s] = -1;
             return s;
         }
     return PB200_ENOMEM;
@@ -943,7 +1302,7 @@ static void ll_drop_graphs(LayerList & ll) {
 }
 static int ll_reserve(pb200_model * m, int T, int nW, int nE) {
     LayerList & ll = *m->ll;
-    const bool grow = T > ll.capT || nW > ll.capW || (size_t) 2 * T + 3 * (size_t) nE + 1 + (size_t) nW + 64 > ll.meta_cap;
+    const bool grow = T > ll.capT || nW > ll.capW || (size_t) 2 * T + 4 * (size_t) nE + 1 + (size_t) nW + 64 > ll.meta_cap;
     if (grow) ll_drop_graphs(ll);   // captured steps hold the addresses of buffers that are about to move
     if (T > ll.capT || nW > ll.capW) {
         CK(cudaStreamSynchronize(m->stream));
@@ -967,6 +1326,16 @@ static int ll_reserve(pb200_model * m, int T, int nW, int nE) {
                 maxact = std::max(maxact, VD);
                 maxbig = std::max(maxbig, 2 * QD + 2 * VD);
                 maxinner = std::max(maxinner, VD);
+            } else if (L.kind == MIX_DUAL) {
+                const DualMix & d = L.dual;
+                const int64_t OD = (int64_t) L.att.heads * L.att.vdim, RV = (int64_t) d.rp.heads * d.rp.vdim;
+                maxact = std::max(maxact, OD + RV);
+                maxact2 = std::max(maxact2, RV);
+                maxbig = std::max<int64_t>(maxbig, d.cols);
+                maxch = std::max<int64_t>(maxch, d.conv_ch);
+                maxinner = std::max(maxinner, RV);
+                maxb2 = std::max(maxb2, OD);                       // the attention result before it is turned back
+                maxb4 = std::max<int64_t>(maxb4, 2 * ll.width);    // the two branch results before they are normed and joined
             } else {
                 const LatentParams & a = L.lat;
                 const int64_t H = a.heads;
@@ -1005,10 +1374,10 @@ static int ll_reserve(pb200_model * m, int T, int nW, int nE) {
         CK(grab(&ll.act, t * (size_t) maxact * es));
         CK(grab(&ll.act2, t * (size_t) maxact2 * es));
         if (ll.frame == FRAME_PRENORM) CK(grab((void **) &ll.hist, (ll.layers.size() + 1) * t * W * 4));
-        if (maxb2) {
-            CK(grab((void **) &ll.big2, t * (size_t) maxb2 * 4)); CK(grab((void **) &ll.big3, t * (size_t) maxb3 * 4));
-            CK(grab((void **) &ll.big4, t * (size_t) maxb4 * 4)); CK(grab((void **) &ll.krb, t * (size_t) std::max<int64_t>(maxkr, 1) * 4));
-        }
+        if (maxb2) CK(grab((void **) &ll.big2, t * (size_t) maxb2 * 4));
+        if (maxb3) CK(grab((void **) &ll.big3, t * (size_t) maxb3 * 4));
+        if (maxb4) CK(grab((void **) &ll.big4, t * (size_t) maxb4 * 4));
+        if (maxkr || maxb3) CK(grab((void **) &ll.krb, t * (size_t) std::max<int64_t>(maxkr, 1) * 4));
         if (moe_top) {
             const size_t pairs = t * (size_t) moe_top;
             CK(grab((void **) &ll.moe_idx, pairs * 4)); CK(grab((void **) &ll.moe_wt, pairs * 4)); CK(grab((void **) &ll.moe_sg, t * 4));
@@ -1030,7 +1399,7 @@ static int ll_reserve(pb200_model * m, int T, int nW, int nE) {
     for (const LLayer & L : ll.layers)
         if (L.kind == MIX_LATENT)
             need_part = std::max(need_part, (size_t) nE * (size_t) latent_decode_splits(ll.n_ctx) * (size_t) L.lat.heads * (size_t) (L.lat.kv_rank + 2));
-        else if (L.kind == MIX_ATTENTION)
+        else if (L.kind == MIX_ATTENTION || L.kind == MIX_DUAL)
             need_part = std::max(need_part, attn_decode_part_floats(L.att, nE));
     if (need_part > ll.lat_part_cap) {
         CK(cudaStreamSynchronize(m->stream));
@@ -1040,7 +1409,7 @@ static int ll_reserve(pb200_model * m, int T, int nW, int nE) {
         CK(cudaMalloc((void **) &ll.lat_part, need_part * 2 * 4));
         ll.lat_part_cap = need_part * 2;
     }
-    const size_t need_meta = (size_t) 2 * T + 3 * (size_t) nE + 1 + (size_t) nW + 64;
+    const size_t need_meta = (size_t) 2 * T + 4 * (size_t) nE + 1 + (size_t) nW + 64;
     if (need_meta > ll.meta_cap) {
         CK(cudaStreamSynchronize(m->stream));
         if (ll.meta_dev) cudaFree(ll.meta_dev);
@@ -1195,6 +1564,93 @@ static int mix_latent(pb200_model * m, const BatchView & b, bool prefill, const 
     return launch_dense(ct, ll.act, VD, L.out.data, VD, out, W, T, W, VD, nullptr, resid, W, 1.f, st);
 }
 
+// ---- dual mixer over ll.act: x[t] += mult * join(attention branch, recurrent branch).  JOIN_SCALED_SUM: both branch results, scaled, lie
+// side by side in ll.act and ONE output product adds them onto the stream.  JOIN_NORMED_MEAN: each branch has its own output product; the
+// two results are normed, averaged and added by one kernel that also leaves rmsnorm(x) * next_norm in ll.act when next_norm is given. ----
+static int mix_dual(pb200_model * m, const BatchView & b, bool prefill, const LRun & r, LLayer & L, float * x, float mult, const float * next_norm) {
+    LayerList & ll = *m->ll;
+    cudaStream_t st = m->stream;
+    const int T = b.n_tokens, W = ll.width, ct = ll.ctype;
+    const AttnParams & a = L.att;
+    const DualMix & d = L.dual;
+    const GatedLinParams & rp = d.rp;
+    const int C = d.cols, OD = a.heads * a.vdim, RV = rp.heads * rp.vdim;
+    const size_t es = esize(ct);
+    // the slot's arena for this run: K rows | V rows | convolution inputs | recurrent state
+    float * kc = ll.state + r.state_off, * vc = kc + (int64_t) a.cache_rows * a.kv_heads * a.dim;
+    int64_t o = (int64_t) a.cache_rows * a.kv_heads * (a.dim + a.vdim);
+    o = (o + 3) / 4 * 4;
+    float * conv_state = ll.state + r.state_off + o;
+    o += (int64_t) std::max(d.taps - 1, 0) * d.conv_ch;
+    o = (o + 3) / 4 * 4;
+    float * rec_state = ll.state + r.state_off + o;
+    CAT(CAT_DENSE);
+    CK(launch_dense(ct, ll.act, W, L.qkvg.data, W, ll.big, C, T, C, W, nullptr, nullptr, 0, 1.f, st));
+    float * src = ll.big;       // where q, k, v of both branches are read from: the projection, or the convolution's output
+    int64_t ld = C;
+    if (d.taps > 0) {
+        CAT(CAT_CONV);
+        CK(launch_causal_conv(ll.big, C, b, d.conv_ch, d.taps, L.dconv_w.data, d.conv_l, conv_state, ll.slot_floats, ll.xbc, d.conv_ch, st));
+        src = ll.xbc;
+        ld = d.conv_ch;
+    }
+    // ---- attention branch ----
+    CAT(CAT_ATTN);
+    AttnPrep pr;
+    pr.norm = d.qk_norm; pr.wq = L.q_norm.data; pr.wk = L.k_norm.data; pr.eps = ll.eps;
+    pr.rot_dims = d.rot_dims; pr.rot_layout = d.rot_layout; pr.rot_freq = L.rot_freq.data;
+    pr.v_rot = d.v_rot; pr.v_layout = d.rot_layout; pr.v_freq = d.v_rot ? L.vrot_freq.data : nullptr;
+    CK(launch_attn_prep_store(src + d.c_q, ld, src + d.c_k, ld, src + d.c_v, ld, b, a, pr, kc, vc, ll.slot_floats, st));
+    AttnIO io;
+    io.q = src + d.c_q; io.ldq = ld;
+    io.k = src + d.c_k; io.ldk = ld;
+    io.v = src + d.c_v; io.ldv = ld;
+    io.k_row = (int64_t) a.kv_heads * a.dim; io.v_row = (int64_t) a.kv_heads * a.vdim;
+    const bool sum = d.join == JOIN_SCALED_SUM;
+    const bool post = d.v_rot || sum;   // the head results are turned back, gated and scaled into their place by a kernel of their own
+    if (!post) { io.gate = ll.big + d.c_g; io.ldg = C; io.gate_mode = d.gate_mode; }
+    void * att_out = post ? (void *) ll.big2 : ll.act;
+    const int att_type = post ? T_F32 : ct;
+    if (prefill) CK(launch_attn_prefill_io(io, b, a, att_out, att_type, st));
+    else CK(launch_attn_decode_io(io, b, a, kc, vc, ll.slot_floats, att_out, att_type, st, ll.lat_part));
+    const int64_t ldo = sum ? OD + RV : OD;
+    if (post)
+        CK(launch_attn_unrotate_gate(ll.big2, b, a.heads, a.vdim, d.rot_layout, d.v_rot ? L.vrot_freq.data : nullptr, ll.big + d.c_g, C, d.gate_mode,
+                                     sum ? d.left_scale : 1.f, ll.act, ldo, ct, st));
+    // ---- recurrent branch ----
+    CAT(CAT_SCAN);
+    GatedLinIO gi;
+    gi.q = src + d.c_rq; gi.ldq = ld;
+    gi.v = src + d.c_rv; gi.ldv = ld;
+    if (d.rec == REC_DELTA) {
+        CK(launch_delta_prep(src + d.c_rq, ld, src + d.c_rk, ld, ll.big + d.c_rb, C, ll.big + d.c_ra, C, L.A_log.data, L.dt_bias.data, rp.qk_heads, rp.heads,
+                             rp.dim, T, st));
+        gi.k = src + d.c_rk; gi.ldk = ld;
+        gi.decay = ll.big + d.c_ra; gi.ldd = C;
+        gi.beta = ll.big + d.c_rb; gi.ldb = C;
+    } else {
+        CK(launch_hgrn2_prep(src + d.c_rq, ld, src + d.c_rk, ld, L.f_bias.data, L.f_lower.data, rp.qk_heads * rp.dim, T, st));
+        gi.decay = src + d.c_rk; gi.ldd = ld;
+    }
+    CK(launch_gated_linattn(gi, b, rp, rec_state, ll.slot_floats, ll.yssm, st));
+    CAT(CAT_NORM);
+    if (sum) {
+        // every head by its own root mean square, the weight all heads share, the SiLU gate, the branch's factor -> beside the attention result
+        CK(launch_norm_gate(ll.yssm, d.rec == REC_DELTA ? ll.big + d.c_rg : nullptr, C, rp.heads, L.onorm.data, d.rec == REC_DELTA ? 1 : -1, ll.eps,
+                            (uint8_t *) ll.act + (size_t) OD * es, ct, T, RV, st, ldo, d.right_scale));
+        CAT(CAT_DENSE);
+        return launch_dense(ct, ll.act, ldo, L.out.data, ldo, x, W, T, W, (int) ldo, nullptr, x, W, mult, st);
+    }
+    CK(launch_norm_gate(ll.yssm, d.rec == REC_DELTA ? ll.big + d.c_rg : nullptr, C, rp.heads, L.onorm.data, d.rec == REC_DELTA ? 1 : -1, ll.eps, ll.act2, ct, T, RV,
+                        st, RV, 1.f));
+    CAT(CAT_DENSE);
+    CK(launch_dense(ct, ll.act, OD, L.out.data, OD, ll.big4, 2 * W, T, W, OD, nullptr, nullptr, 0, 1.f, st));
+    CK(launch_dense(ct, ll.act2, RV, L.out_r.data, RV, ll.big4 + W, 2 * W, T, W, RV, nullptr, nullptr, 0, 1.f, st));
+    CAT(CAT_NORM);
+    return launch_rmsnorm_pair_residual(ll.big4, 2 * W, ll.big4 + W, 2 * W, L.join_wl.data, L.join_wr.data, mult * d.left_scale, ll.eps, x, next_norm,
+                                        next_norm ? ll.act : nullptr, ct, T, W, st);
+}
+
 // ---- clamped gated feed-forward: x[t] += down(glu(gateup(ll.act[t]))); ll.act stays as it is ----
 static int ff_clamped(pb200_model * m, int T, const DenseW & gateup, const DenseW & down, int ff, float limit, float * x) {
     LayerList & ll = *m->ll;
@@ -1221,7 +1677,7 @@ static int ff_relu2(pb200_model * m, int T, const DenseW & up, const DenseW & do
 }
 // ---- mixture of experts over ll.act.  accumulate: x[t] += shared(h) + sum_k w_k expert_k(h) (the stream itself); otherwise x receives the
 // sublayer's result alone.  The router form and the expert form come from the layer (LLayer::route, MoeParams::act). ----
-static int ff_moe(pb200_model * m, int T, bool prefill, LLayer & L, float * x, bool accumulate) {
+static int ff_moe(pb200_model * m, int T, bool prefill, LLayer & L, float * x, bool accumulate, float out_scale = 1.f) {
     LayerList & ll = *m->ll;
     cudaStream_t st = m->stream;
     const int W = ll.width, ct = ll.ctype;
@@ -1242,19 +1698,26 @@ static int ff_moe(pb200_model * m, int T, bool prefill, LLayer & L, float * x, b
         } else {
             base = MOE_SET;
         }
+    } else if (L.route == ROUTE_SIGMOID_PLAIN) {   // plain sigmoid scores: no correction, no groups, the chosen scores are the weights
+        CK(launch_moe_route_sigmoid(ll.act, ct, L.router.data, nullptr, p, W, nullptr, ll.moe_idx, ll.moe_wt, nullptr, T, st));
+        if (L.shared_ff > 0 || p.act != 2) return PB200_ENOTSUP;
+        if (!accumulate) base = MOE_SET;
     } else {
         CK(launch_moe_route(ll.act, ct, L.router.data, L.router_b.data, p, W, ll.moe_idx, ll.moe_wt, T, st));
         if (!accumulate || p.act != 0) return PB200_ENOTSUP;
         if (L.shared_ff > 0) CK(ff_clamped(m, T, L.s_gateup, L.s_down, L.shared_ff, L.shared_limit, x));
     }
+    // a weight on the expert's input rides on the gate / up products; the sum over the experts then takes none
+    const float * in_wt = p.weight_on_input ? ll.moe_wt : nullptr, * sum_wt = p.weight_on_input ? nullptr : ll.moe_wt;
     auto activate = [&](int rows) -> int {
         if (p.act == 1) return launch_relu2(ll.moe_gu, ll.moe_y, ct, (int64_t) rows * p.ff, st);
+        if (p.act == 2) return launch_silu_mul(ll.moe_gu, ll.moe_y, ct, rows, p.ff, in_wt, ll.moe_perm, st);
         return launch_clamped_glu(ll.moe_gu, ll.moe_y, ct, rows, p.ff, p.limit, st);
     };
     CAT(CAT_MOE);
     if (!prefill || (int64_t) T * p.top <= 64) {
-        CK(launch_moe_gateup_rows(ll.act, ct, L.e_gateup.data, ll.moe_idx, p, W, ll.moe_y, T, st));
-        return launch_moe_down_rows(ll.moe_y, ct, L.e_down.data, ll.moe_idx, ll.moe_wt, p, W, x, T, st, base, xscale);
+        CK(launch_moe_gateup_rows(ll.act, ct, L.e_gateup.data, ll.moe_idx, p, W, ll.moe_y, T, st, in_wt));
+        return launch_moe_down_rows(ll.moe_y, ct, L.e_down.data, ll.moe_idx, sum_wt, p, W, x, T, st, base, xscale, out_scale);
     }
     const int P = T * p.top, E = p.experts;
     CK(launch_moe_sort(ll.moe_idx, p, T, ll.moe_count, ll.moe_start, ll.moe_perm, st));
@@ -1265,7 +1728,7 @@ static int ff_moe(pb200_model * m, int T, bool prefill, LLayer & L, float * x, b
         CK(launch_dense_grouped(ct, ll.moe_hs, W, L.e_gateup.data, W, (int64_t) UR * W, ll.moe_gu, UR, ll.moe_start, ll.moe_count, E, P, UR, W, st));
         CK(activate(P));
         CK(launch_dense_grouped(ct, ll.moe_y, p.ff, L.e_down.data, p.ff, (int64_t) W * p.ff, ll.moe_ds, W, ll.moe_start, ll.moe_count, E, P, W, p.ff, st));
-        return launch_moe_combine(ll.moe_ds, ll.moe_perm, ll.moe_row_of, ll.moe_wt, p.top, W, x, T, st, base, xscale);
+        return launch_moe_combine(ll.moe_ds, ll.moe_perm, ll.moe_row_of, sum_wt, p.top, W, x, T, st, base, xscale, out_scale);
     }
     CK(cudaMemcpyAsync(ll.moe_count_host, ll.moe_count, (size_t) E * 4, cudaMemcpyDeviceToHost, st));
     CK(cudaMemcpyAsync(ll.moe_count_host + 4096, ll.moe_start, (size_t) E * 4, cudaMemcpyDeviceToHost, st));
@@ -1280,7 +1743,7 @@ static int ff_moe(pb200_model * m, int T, bool prefill, LLayer & L, float * x, b
         if (cnt[e] > 0)
             CK(launch_dense(ct, (const uint8_t *) ll.moe_y + (size_t) start[e] * p.ff * es, p.ff, (const uint8_t *) L.e_down.data + (size_t) e * W * p.ff * es, p.ff,
                             ll.moe_ds + (int64_t) start[e] * W, W, cnt[e], W, p.ff, nullptr, nullptr, 0, 1.f, st));
-    return launch_moe_combine(ll.moe_ds, ll.moe_perm, ll.moe_row_of, ll.moe_wt, p.top, W, x, T, st, base, xscale);
+    return launch_moe_combine(ll.moe_ds, ll.moe_perm, ll.moe_row_of, sum_wt, p.top, W, x, T, st, base, xscale, out_scale);
 }
 
 // FRAME_POSTNORM: the stream starts as embedding + position vector; x <- x + mult * LN(mixer(x)), x <- x + mult * LN(ff(x)) with weight
@@ -1314,6 +1777,56 @@ static int ll_forward_postnorm(pb200_model * m, const BatchView & b, bool prefil
         float * lg = ll.logits + (int64_t) lrow0 * ll.vocab;
         CK(launch_dense(ct, ll.actw, W, ll.head.data, W, lg, ll.vocab, nW, ll.vocab, W, nullptr, nullptr, 0, ll.logit_scale, st));
         CK(launch_softcap(lg, (int64_t) nW * ll.vocab, ll.logit_softcap, st));
+    }
+    CAT(-1);
+    return 0;
+}
+
+// FRAME_PRERMS: the stream starts as embed * scale + bigram row; x <- x + mult * mixer(norm1 x), x <- x + mult * ff(norm2 x) with RMS norms of
+// one learned number (kept as a constant vector); every pass of the repeated block first adds the embedding output (not the first pass) and
+// its step vector.  ll.act holds the next sublayer's normed input in the operand type.
+static int ll_forward_prerms(pb200_model * m, const BatchView & b, bool prefill, const int32_t * tokens_dev, const int32_t * want_dev, int nW, int lrow0) {
+    LayerList & ll = *m->ll;
+    cudaStream_t st = m->stream;
+    const int T = b.n_tokens, W = ll.width, ct = ll.ctype;
+    CAT(CAT_ELEM);
+    CK(launch_embed_bigram(ll.embed.data, ll.bigram.buckets > 0 ? ll.bigram_table.data : nullptr, ct, W, ll.embed_scale, ll.bigram, tokens_dev, b, ll.x,
+                           ll.loop_times > 1 ? ll.x0 : nullptr, st));
+    bool act_ready = false;   // the kernel that closed the previous sublayer has left this one's normed input in ll.act
+    for (size_t ir = 0; ir < ll.runs.size(); ir++) {
+        const LRun & r = ll.runs[ir];
+        LLayer & L = ll.layers[(size_t) r.layer];
+        if (L.kind != MIX_DUAL) return PB200_ENOTSUP;
+        if (r.pass >= 0) {
+            CAT(CAT_NORM);
+            CK(launch_stream_add_rmsnorm(ll.x, r.pass > 0 ? ll.x0 : nullptr, ll.loop_step.data + (int64_t) r.pass * W, L.norm1.data, ll.eps, ll.act, ct, T, W, st));
+        } else if (!act_ready) {
+            CAT(CAT_NORM);
+            CK(launch_group_rmsnorm(ll.x, nullptr, L.norm1.data, 1, ll.eps, ll.act, ct, T, W, st));
+        }
+        act_ready = false;
+        // the norm that follows the mixer: this layer's second one, or the next run's first one unless that run opens a pass
+        const float * next_norm = nullptr;
+        if (L.ff > 0) next_norm = L.norm2.data;
+        else if (ir + 1 < ll.runs.size() && ll.runs[ir + 1].pass < 0) next_norm = ll.layers[(size_t) ll.runs[ir + 1].layer].norm1.data;
+        CK(mix_dual(m, b, prefill, r, L, ll.x, ll.resid_mult, next_norm));
+        const bool fused = L.dual.join == JOIN_NORMED_MEAN && next_norm;
+        if (L.ff > 0) {
+            if (!fused) {
+                CAT(CAT_NORM);
+                CK(launch_group_rmsnorm(ll.x, nullptr, L.norm2.data, 1, ll.eps, ll.act, ct, T, W, st));
+            }
+            if (L.ff_kind != FF_MOE) return PB200_ENOTSUP;
+            CK(ff_moe(m, T, prefill, L, ll.x, true, ll.resid_mult));
+        } else {
+            act_ready = fused;
+        }
+        if (ll.tap_on) CK(cudaMemcpyAsync(ll.tap + (int64_t) ir * T * W, ll.x, (size_t) T * W * 4, cudaMemcpyDeviceToDevice, st));
+    }
+    if (nW > 0) {
+        CAT(CAT_HEAD);
+        CK(launch_group_rmsnorm(ll.x, want_dev, ll.final_norm.data, 1, ll.eps, ll.actw, ct, nW, W, st));
+        CK(launch_dense(ct, ll.actw, W, ll.head.data, W, ll.logits + (int64_t) lrow0 * ll.vocab, ll.vocab, nW, ll.vocab, W, nullptr, nullptr, 0, ll.logit_scale, st));
     }
     CAT(-1);
     return 0;
@@ -1377,6 +1890,7 @@ static int ll_forward(pb200_model * m, const BatchView & b, bool prefill, const 
     CK(tap_prepare(m, b.n_tokens));
     if (ll.frame == FRAME_PRENORM) return ll_forward_prenorm(m, b, prefill, tokens_dev, want_dev, nW, lrow0);
     if (ll.frame == FRAME_POSTNORM) return ll_forward_postnorm(m, b, prefill, tokens_dev, want_dev, nW, lrow0);
+    if (ll.frame == FRAME_PRERMS) return ll_forward_prerms(m, b, prefill, tokens_dev, want_dev, nW, lrow0);
     CAT(CAT_ELEM);
     const int T = b.n_tokens, W = ll.width, ct = ll.ctype;
     CK(launch_embed(ll.embed.data, ct, W, tokens_dev, T, ll.x, ll.x0, st));
@@ -1454,7 +1968,7 @@ static int ll_run_sub(pb200_model * m, std::vector<SubEntry> & es, bool prefill)
     int T = 0, nW = 0, max_n = 0;
     for (const SubEntry & e : es) { T += e.n; nW += (int) e.want.size(); max_n = std::max(max_n, e.n); }
     CK(ll_reserve(m, T, nW, nE));
-    // meta layout: tokens[T] | entry_of[T] | slot[nE] | off[nE+1] | pos0[nE] | want[nW]
+    // meta layout: tokens[T] | entry_of[T] | slot[nE] | off[nE+1] | pos0[nE] | want[nW] | prev[nE]
     int32_t * h = ll.meta_host;
     int32_t *h_tok = h, *h_ent = h + T, *h_slot = h + 2 * T, *h_off = h_slot + nE, *h_pos = h_off + nE + 1, *h_want = h_pos + nE;
     int t = 0;
@@ -1470,12 +1984,14 @@ static int ll_run_sub(pb200_model * m, std::vector<SubEntry> & es, bool prefill)
     int w = 0;
     for (int i = 0; i < nE; i++)
         for (const auto & pr : es[(size_t) i].want) { h_want[w++] = h_off[i] + pr.first; lrows.push_back(pr.second); }
-    const size_t total = (size_t) (h_want + nW - h);
+    int32_t * h_prev = h_want + nW;   // the token before each entry's first one (-1: none)
+    for (int i = 0; i < nE; i++) h_prev[i] = es[(size_t) i].pos0 > 0 ? ll.seq_prev[(size_t) es[(size_t) i].slot] : -1;
+    const size_t total = (size_t) (h_prev + nE - h);
     int32_t * d = ll.meta_dev;
     CK(cudaMemcpyAsync(d, h, total * 4, cudaMemcpyHostToDevice, m->stream));
     BatchView b;
     b.n_entries = nE; b.n_tokens = T; b.max_n = max_n;
-    b.slot = d + 2 * T; b.off = b.slot + nE; b.pos0 = b.off + nE + 1; b.entry_of = d + T;
+    b.slot = d + 2 * T; b.off = b.slot + nE; b.pos0 = b.off + nE + 1; b.entry_of = d + T; b.prev = d + (h_prev - h);
     static const bool no_graph = getenv("PB200_NO_STEP_GRAPH") != nullptr;
     bool ran = false;
     if (!prefill && m->use_graph && !no_graph && !ll.tap_on && !ll.prof_on && T == nE) {
@@ -1505,7 +2021,11 @@ static int ll_run_sub(pb200_model * m, std::vector<SubEntry> & es, bool prefill)
     CK(cudaStreamSynchronize(m->stream));
     CK(prof_collect(m));
     // hand the rows to the caller's order
-    for (int i = 0; i < nE; i++) ll.seq_len[(size_t) es[(size_t) i].slot] = es[(size_t) i].pos0 + es[(size_t) i].n;
+    for (int i = 0; i < nE; i++) {
+        const SubEntry & e = es[(size_t) i];
+        ll.seq_len[(size_t) e.slot] = e.pos0 + e.n;
+        ll.seq_prev[(size_t) e.slot] = e.tokens[e.n - 1];
+    }
     ll.rows_tmp.assign(lrows.begin(), lrows.end());
     return 0;
 }

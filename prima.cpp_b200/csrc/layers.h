@@ -5,7 +5,10 @@
 // fixed decay per head; softmax attention over a low-rank latent with a shared rotated key part; the clamped gated feed-forward, dense
 // or as a routed mixture of experts; layer norm with weight and bias on a sublayer's result (post-norm frame), a learned position table,
 // an RMS norm per query / key head, the squared-ReLU feed-forward, the router with sigmoid scores, a choice correction and expert groups,
-// and the tanh soft-cap of the logits.  Every constant of a mechanism is a parameter, nothing is tied to one model.
+// and the tanh soft-cap of the logits; a hashed bigram embedding, a short causal convolution over any range of projection channels, the
+// preparation of attention inputs (RMS norm over a whole projection or per head, partial rotation in either pair layout, values rotated by
+// their position), a sink in the softmax denominator, gated linear recurrences with a decay per token (gated delta rule, HGRN2), experts
+// whose routing weight multiplies their input.  Every constant of a mechanism is a parameter, nothing is tied to one model.
 // All launchers enqueue on `stream` and return a cudaError_t as int (0 = success).
 #pragma once
 #include <cuda_bf16.h>
@@ -26,6 +29,7 @@ struct BatchView {
     const int32_t * off = nullptr;    // device [n_entries + 1]
     const int32_t * pos0 = nullptr;   // device [n_entries]
     const int32_t * entry_of = nullptr;   // device [n_tokens]
+    const int32_t * prev = nullptr;       // device [n_entries]: the sequence's token before the entry's first one (-1: the entry starts the sequence)
 };
 
 // ---- dense products ----
@@ -48,6 +52,12 @@ int launch_embed(const void * table, int type, int width, const int32_t * tokens
 // x[t] = table[tokens[t]] + pos_table[position of t] (fp32 sum; both tables in `type`); xa (if given) receives x in the operand type
 int launch_embed_pos(const void * table, const void * pos_table, int type, int width, const int32_t * tokens, const BatchView & b, float * x, void * xa,
                      int otype, cudaStream_t stream);
+// x[t] = table[tokens[t]] * scale + bigram[row], row = (previous token * mul_prev + tokens[t] * mul_cur) mod buckets, or row `buckets` for a
+// sequence's first token (bigram == nullptr: no second table).  The previous token of an entry's first token is b.prev.  x0 (may be null)
+// receives a copy.
+struct BigramParams { int64_t buckets = 0, mul_prev = 0, mul_cur = 0; };
+int launch_embed_bigram(const void * table, const void * bigram, int type, int width, float scale, const BigramParams & bg, const int32_t * tokens,
+                        const BatchView & b, float * x, float * x0, cudaStream_t stream);
 int launch_cast(const float * x, void * y, int otype, int64_t n, cudaStream_t stream);
 // y[r] = (x[row] - mean) / sqrt(var + eps) * w, row = rows ? rows[r] : r; var = mean of squared deviations
 int launch_layernorm(const float * x, const int32_t * rows, const float * w, float eps, void * y, int otype, int n_rows, int width, cudaStream_t stream);
@@ -82,6 +92,7 @@ struct AttnParams {
     int cache_rows = 0;       // rows per slot: positions < keep_first at their own row, later ones in a ring over the rest
     int shared_dim = 0;       // prompt kernels: the last shared_dim of a key's dim entries come from one array all heads share
     int gated = 1;            // the fused projection ends with one gate logit per head (0: q | k | v only, the output is not gated)
+    int sink = 0;             // 1: one is added to the softmax denominator (a key of score 0 that has no value)
 };
 // Where the attention kernels read their inputs (fp32 rows, strides in floats).  Prompt kernels read keys and values of the batch:
 // k rows hold [kv_heads][dim - shared_dim], ks rows [shared_dim]; v rows [kv_heads][vdim].  Decode kernels read q and gate here and
@@ -178,8 +189,9 @@ struct DecayAttnParams {
 int launch_decay_attn(const float * qkv, int64_t ld, int q_off, int k_off, int v_off, const BatchView & b, const DecayAttnParams & p, const float * decay,
                       float * state, int64_t slot_stride, float * y, cudaStream_t stream);
 // out[t] = y[t] / rms over each of `groups` consecutive parts (* w if w) * act(gate[t]);  act: 0 sigmoid, 1 silu;  gate rows ldg floats apart
+// gate_act -1 (or gate == nullptr): no gate.  The result, times out_scale, goes to rows of ldo elements (0: inner).
 int launch_norm_gate(const float * y, const float * gate, int64_t ldg, int groups, const float * w, int gate_act, float eps, void * out, int otype,
-                     int n_tokens, int inner, cudaStream_t stream);
+                     int n_tokens, int inner, cudaStream_t stream, int64_t ldo = 0, float out_scale = 1.f);
 
 // ---- attention over a latent ----
 struct LatentParams {
@@ -221,35 +233,110 @@ int launch_clamped_glu(const float * gu, void * y, int otype, int n_tokens, int 
 struct MoeParams {
     int experts = 0, top = 0, ff = 0;
     float limit = 0.f;
-    int act = 0;              // expert form: 0 = clamped gated unit (rows gate | up, 2 ff per expert), 1 = max(up, 0)^2 (rows up, ff per expert)
+    int act = 0;              // expert form: 0 = clamped gated unit (rows gate | up, 2 ff per expert), 1 = max(up, 0)^2 (rows up, ff per expert),
+                              // 2 = SiLU gated unit silu(gate) * up (rows gate | up)
+    int weight_on_input = 0;  // 1: a chosen expert's weight multiplies its INPUT (applied to the gate / up products, which are linear in it);
+                              // the sum over the experts then takes no weights
+    int norm_weights = 1;     // launch_moe_route_sigmoid: 1 = the chosen scores divided by their sum, 0 = the plain scores
     int groups = 1, keep_groups = 1;   // launch_moe_route_sigmoid: equal groups of neighbouring experts, of which the best keep_groups stay eligible
     float route_scale = 1.f;           // launch_moe_route_sigmoid: factor on the normalised weights
 };
-__host__ __device__ inline int moe_up_rows(const MoeParams & p) { return p.act == 0 ? 2 * p.ff : p.ff; }
+__host__ __device__ inline int moe_up_rows(const MoeParams & p) { return p.act == 1 ? p.ff : 2 * p.ff; }
 // z = h W_r^T + bias in fp32 (h: the operand-type activations); idx[t][0..top) the experts with the largest z (ties: lower index),
 // wt[t][..] the softmax over the chosen logits
 int launch_moe_route(const void * h, int htype, const float * wr, const float * bias, const MoeParams & p, int width, int32_t * idx, float * wt,
                      int n_tokens, cudaStream_t stream);
 // s = sigmoid(h W_r^T) in fp32; choice score c = s + correction; score of a group = its two largest c summed (its only one in a group of
 // one); experts outside the keep_groups best groups are not eligible; idx[t][0..top) the eligible experts with the largest c (ties: lower
-// index), wt[t][k] = s[idx] / (sum of the chosen s + 1e-20) * route_scale.  shared_gate (may be null, then sg_out is not written):
+// index), wt[t][k] = s[idx] / (sum of the chosen s + 1e-20) * route_scale (norm_weights 0: s[idx] * route_scale).  correction may be null.
+// shared_gate (may be null, then sg_out is not written):
 // sg_out[t] = sigmoid(h . shared_gate), the factor on a shared expert's result.
 int launch_moe_route_sigmoid(const void * h, int htype, const float * wr, const float * correction, const MoeParams & p, int width, const float * shared_gate,
                              int32_t * idx, float * wt, float * sg_out, int n_tokens, cudaStream_t stream);
 // few tokens: every (token, chosen expert) streams its expert's rows.  y[t][k][ff] = act(expert idx[t][k] of gateup) -> operand type
+// in_wt (weight_on_input): the pair's weight, a factor on its gate and up products
 int launch_moe_gateup_rows(const void * h, int type, const void * gateup, const int32_t * idx, const MoeParams & p, int width, void * y, int n_tokens,
-                           cudaStream_t stream);
+                           cudaStream_t stream, const float * in_wt = nullptr);
+// y[r][j] = silu(s gu[r][j]) * (s gu[r][ff + j]),  s = in_wt ? in_wt[perm ? perm[r] : r] : 1      gu: [rows][2 ff] f32
+int launch_silu_mul(const float * gu, void * y, int otype, int n_rows, int ff, const float * in_wt, const int32_t * perm, cudaStream_t stream);
 // x[t] = base(x[t]) + sum_k wt[t][k] * down[idx[t][k]] y[t][k]      (k in the order of the choice)
 // base: MOE_ADD x[t] itself, MOE_SET zero, MOE_SCALE x[t] * xscale[t] (a gated shared expert's result waits in x)
 enum : int { MOE_ADD = 0, MOE_SET = 1, MOE_SCALE = 2 };
+// wt == nullptr: every weight is one.  The sum is multiplied by out_scale before it meets the base.
 int launch_moe_down_rows(const void * y, int type, const void * down, const int32_t * idx, const float * wt, const MoeParams & p, int width, float * x,
-                         int n_tokens, cudaStream_t stream, int base = MOE_ADD, const float * xscale = nullptr);
+                         int n_tokens, cudaStream_t stream, int base = MOE_ADD, const float * xscale = nullptr, float out_scale = 1.f);
 // many tokens: pairs (t, k) sorted by expert (stable).  count[e], start[e] (exclusive prefix), perm[r] = pair index t * top + k of sorted row r
 int launch_moe_sort(const int32_t * idx, const MoeParams & p, int n_tokens, int32_t * count, int32_t * start, int32_t * perm, cudaStream_t stream);
 // hs[r] = h[perm[r] / top]   (rows of `width` operand-type elements)
 int launch_moe_gather(const void * h, int type, const int32_t * perm, int top, int width, void * hs, int n_rows, cudaStream_t stream);
 // x[t] = base(x[t]) + sum_k wt[t][k] * ds[row_of[t * top + k]],  row_of = inverse of perm (computed by the kernel from perm)
 int launch_moe_combine(const float * ds, const int32_t * perm, int32_t * row_of, const float * wt, int top, int width, float * x, int n_tokens,
-                       cudaStream_t stream, int base = MOE_ADD, const float * xscale = nullptr);
+                       cudaStream_t stream, int base = MOE_ADD, const float * xscale = nullptr, float out_scale = 1.f);
+
+// ---- short causal convolution over a range of projection channels ----
+// out[t][c] = act(sum_j w[c][j] * in(t - taps + 1 + j)[c]), c < channels, in(t) = u[t * ldu + c]; inputs before the entry's first token come
+// from the slot's state [taps - 1][channels] (zeros for a new sequence), which then advances to the entry's last taps - 1 inputs.  No bias.
+// act: channels >= silu_from pass SiLU, the ones below none.  w: [channels][taps].
+int launch_causal_conv(const float * u, int64_t ldu, const BatchView & b, int channels, int taps, const float * w, int silu_from, float * conv_state,
+                       int64_t slot_stride, float * out, int64_t ldo, cudaStream_t stream);
+
+// ---- preparation of attention inputs, in place, and the cache store ----
+enum : int { ROT_INTERLEAVED = 0, ROT_HALVES = 1 };   // pair (2i, 2i + 1), or (i, i + dims / 2)
+enum : int { QKN_NONE = 0, QKN_HEAD_UNIT = 1, QKN_WHOLE_WEIGHT = 2 };
+struct AttnPrep {
+    int norm = QKN_NONE;          // QKN_HEAD_UNIT: every query / key head divided by its root mean square AFTER the rotation, no weight;
+                                  // QKN_WHOLE_WEIGHT: RMS norm over all query rows at once (and all key rows) with weights wq / wk, BEFORE the rotation
+    const float * wq = nullptr, * wk = nullptr;   // [heads * dim], [kv_heads * dim]
+    float eps = 0.f;
+    int rot_dims = 0;             // the leading rot_dims entries of every query / key head turn by position * rot_freq[i]
+    int rot_layout = ROT_INTERLEAVED;
+    const float * rot_freq = nullptr;   // [rot_dims / 2]
+    int v_rot = 0;                // 1: every value head turns by its position over all vdim entries (pairs in v_layout, v_freq [vdim / 2]);
+    int v_layout = ROT_INTERLEAVED;     // the cache holds the turned values and launch_attn_unrotate_gate turns a head's result back
+    const float * v_freq = nullptr;
+};
+// q [T][heads][dim], k [T][kv_heads][dim], v [T][kv_heads][vdim] (rows ldq / ldk / ldv floats apart) are prepared in place; then the K / V
+// rows that later tokens can still see go to the cache (layout as launch_attn_kv_store).
+int launch_attn_prep_store(float * q, int64_t ldq, float * k, int64_t ldk, float * v, int64_t ldv, const BatchView & b, const AttnParams & a,
+                           const AttnPrep & pr, float * kcache, float * vcache, int64_t slot_stride, cudaStream_t stream);
+// o [T][heads][vdim] f32 (an attention result over values turned by their positions): every head is turned back by the token's position
+// (v_freq == nullptr: not turned), multiplied by sigmoid of its gate logit (gate_mode as in AttnIO) and by out_scale -> out rows of ldo
+// elements in the operand type
+int launch_attn_unrotate_gate(const float * o, const BatchView & b, int heads, int vdim, int v_layout, const float * v_freq, const float * gate, int64_t ldg,
+                              int gate_mode, float out_scale, void * out, int64_t ldo, int otype, cudaStream_t stream);
+
+// ---- gated linear recurrences: a state S [dim][vdim] f32 per (sequence slot, head) with a decay that every token brings ----
+//   decay_per_channel 0: S <- g S (g [T][heads]);  1: S <- diag(f) S (f [T][qk_heads][dim])
+//   delta 0: S <- S + k v^T;   1 (delta rule): u = beta (v - S^T k), S <- S + k u^T (beta [T][heads]), after the decay
+//   tied_key 1: k = 1 - f (needs decay_per_channel; io.k unused)
+//   y = S^T q, after the token's write.        Head h reads q / k head h / (heads / qk_heads).
+struct GatedLinParams {
+    int heads = 0, qk_heads = 0, dim = 0, vdim = 0;
+    int decay_per_channel = 0, delta = 0, tied_key = 0;
+};
+struct GatedLinIO {
+    const float * q = nullptr;      int64_t ldq = 0;    // [qk_heads][dim]
+    const float * k = nullptr;      int64_t ldk = 0;
+    const float * v = nullptr;      int64_t ldv = 0;    // [heads][vdim]
+    const float * decay = nullptr;  int64_t ldd = 0;
+    const float * beta = nullptr;   int64_t ldb = 0;
+};
+int launch_gated_linattn(const GatedLinIO & io, const BatchView & b, const GatedLinParams & p, float * state, int64_t slot_stride, float * y,
+                         cudaStream_t stream);
+// inputs of the gated delta rule, in place: every q / k head (qk_heads of each, dim wide) becomes x / sqrt(sum x^2 + 1e-6), q also times
+// dim^-1/2;  beta <- sigmoid(beta);  a <- exp(-exp(A_log[h]) * softplus(a + dt_bias[h]))    (beta, a: [T][heads])
+int launch_delta_prep(float * q, int64_t ldq, float * k, int64_t ldk, float * beta, int64_t ldb, float * a, int64_t lda, const float * A_log,
+                      const float * dt_bias, int qk_heads, int heads, int dim, int n_tokens, cudaStream_t stream);
+// inputs of HGRN2, in place: q <- silu(q);  f <- lower + (1 - lower) * sigmoid(f + f_bias)      (n = heads * dim entries per token)
+int launch_hgrn2_prep(float * q, int64_t ldq, float * f, int64_t ldf, const float * f_bias, const float * lower, int n, int n_tokens, cudaStream_t stream);
+
+// x[t] += (x0 ? x0[t] : 0) + (vec ? vec : 0), then y[t] = rmsnorm(x[t]) * w in the operand type: what opens a pass of a repeated block whose
+// passes add the embedding output and a step vector, with the first layer's norm
+int launch_stream_add_rmsnorm(float * x, const float * x0, const float * vec, const float * w, float eps, void * y, int otype, int n_rows, int width,
+                              cudaStream_t stream);
+// x[t] += mult * (rmsnorm(a[t]) * wa + rmsnorm(b[t]) * wb), then y[t] = rmsnorm(x[t]) * wn in the operand type (y may be null): two branch
+// results joined after a norm each, the residual sum and the next sublayer's input in one pass.  a, b rows lda / ldb floats apart.
+int launch_rmsnorm_pair_residual(const float * a, int64_t lda, const float * bb, int64_t ldb, const float * wa, const float * wb, float mult, float eps,
+                                 float * x, const float * wn, void * y, int otype, int n_rows, int width, cudaStream_t stream);
 
 }  // namespace pb

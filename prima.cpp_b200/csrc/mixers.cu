@@ -330,6 +330,7 @@ __global__ void __launch_bounds__(AQ * 32) k_attn_window_prefill(const AttnIO io
         }
     }
     if (!qok) return;
+    if (a.sink && m != -INFINITY) l += expf(-m);   // the sink: a key of score 0 in the denominator only
     const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
     for (int c = 0; c < NV; c++) {
@@ -479,6 +480,7 @@ __global__ void __launch_bounds__(256) k_attn_window_prefill_tiled(const AttnIO 
     for (int i = 0; i < 4; i++) {
         const int qi = q0 + ty * 4 + i;
         if (qi >= n) continue;
+        if (a.sink && m[i] != -INFINITY) l[i] += expf(-m[i]);
         const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
 #pragma unroll
         for (int c = 0; c < NVC; c++) {
@@ -608,6 +610,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) k_attn_window_decode(const Att
             }
             return;
         }
+        if (a.sink && M != -INFINITY) L += expf(-M);
         const float inv = L > 0.f ? 1.f / L : 0.f;
 #pragma unroll
         for (int c = 0; c < NV; c++) {
@@ -631,6 +634,7 @@ __global__ void __launch_bounds__(128) k_attn_decode_merge(const AttnIO io, cons
         const float ms = pp[(int64_t) s * (DV + 2)];
         if (ms != -INFINITY) L += pp[(int64_t) s * (DV + 2) + 1] * expf(ms - M);
     }
+    if (a.sink && M != -INFINITY) L += expf(-M);
     const float inv = L > 0.f ? 1.f / L : 0.f;
     for (int d = threadIdx.x; d < DV; d += blockDim.x) {
         float o = 0.f;

@@ -1,5 +1,5 @@
-// prima.cpp_b200/csrc/moe.cu — routed mixture of experts (declarations and semantics: layers.h).  An expert is a clamped gated unit or a
-// squared-ReLU unit (MoeParams::act).  The router runs in fp32, in one of two forms: logits + bias, the `top` largest (ties: the lower
+// prima.cpp_b200/csrc/moe.cu — routed mixture of experts (declarations and semantics: layers.h).  An expert is a clamped gated unit, a
+// squared-ReLU unit or a SiLU gated unit (MoeParams::act); its routing weight multiplies its result or its input (weight_on_input).  The router runs in fp32, in one of two forms: logits + bias, the `top` largest (ties: the lower
 // index), softmax over the chosen logits (k_moe_route); or sigmoid scores, a per-expert correction added for the choice only, the choice
 // limited to the best groups of neighbouring experts, weights = the uncorrected scores of the chosen divided by their sum, times a factor
 // (k_moe_route_sigmoid, which also yields the sigmoid gate of a shared expert).  Two ways through the experts:
@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(1024) k_moe_route_sigmoid(const HT * __restric
             if (lane == 0) sg_out[t] = sigmoid_f(acc);
         } else {
             const float acc = wsum(dot_lane8(wr + (int64_t) e * width, hs, width, lane));
-            if (lane == 0) { const float s = sigmoid_f(acc); sc[e] = s; ch[e] = s + corr[e]; }
+            if (lane == 0) { const float s = sigmoid_f(acc); sc[e] = s; ch[e] = corr ? s + corr[e] : s; }
         }
     }
     __syncthreads();
@@ -168,13 +168,13 @@ __global__ void __launch_bounds__(1024) k_moe_route_sigmoid(const HT * __restric
         __syncwarp();
     }
     const float sum = wsum(lane < p.top ? mine : 0.f);
-    if (lane < p.top) wt[(int64_t) t * p.top + lane] = mine / (sum + 1e-20f) * p.route_scale;
+    if (lane < p.top) wt[(int64_t) t * p.top + lane] = (p.norm_weights ? mine / (sum + 1e-20f) : mine) * p.route_scale;
 }
 
 // grid (ceil(ff / 8), pairs): warp -> row j of gate and of up of the pair's expert
 template <typename WT, bool VEC>
 __global__ void __launch_bounds__(256) k_moe_gateup_rows(const WT * __restrict__ h, const WT * __restrict__ gateup, const int32_t * __restrict__ idx, MoeParams p,
-                                                         int width, WT * __restrict__ y) {
+                                                         int width, WT * __restrict__ y, const float * __restrict__ in_wt) {
     const int pair = blockIdx.y, t = pair / p.top;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int j = blockIdx.x * 8 + warp;
@@ -191,16 +191,21 @@ __global__ void __launch_bounds__(256) k_moe_gateup_rows(const WT * __restrict__
     g = wsum(g);
     u = wsum(u);
     if (lane == 0) {
-        g = fminf(g, p.limit);
-        u = fminf(fmaxf(u, -p.limit), p.limit);
-        put(y, (int64_t) pair * p.ff + j, g * sigmoid_f(1.702f * g) * (u + 1.f));
+        if (in_wt) { g *= in_wt[pair]; u *= in_wt[pair]; }   // the weight on the expert's input, applied to the products that are linear in it
+        if (p.act == 2) {
+            put(y, (int64_t) pair * p.ff + j, silu_f(g) * u);
+        } else {
+            g = fminf(g, p.limit);
+            u = fminf(fmaxf(u, -p.limit), p.limit);
+            put(y, (int64_t) pair * p.ff + j, g * sigmoid_f(1.702f * g) * (u + 1.f));
+        }
     }
 }
 // grid (ceil(width / 8), tokens): warp -> output n of the token, summed over its experts in the order of the choice
 template <typename WT, bool VEC>
 __global__ void __launch_bounds__(256) k_moe_down_rows(const WT * __restrict__ y, const WT * __restrict__ down, const int32_t * __restrict__ idx,
                                                        const float * __restrict__ wt, MoeParams p, int width, float * __restrict__ x, int base,
-                                                       const float * __restrict__ xscale) {
+                                                       const float * __restrict__ xscale, float out_scale) {
     const int t = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x * 8 + warp;
@@ -210,11 +215,11 @@ __global__ void __launch_bounds__(256) k_moe_down_rows(const WT * __restrict__ y
         const int pair = t * p.top + k;
         const WT * w = down + ((int64_t) idx[pair] * width + n) * p.ff;
         const float d = wsum(dot_part<WT, VEC>(w, y + (int64_t) pair * p.ff, p.ff, lane));
-        acc = fmaf(wt[pair], d, acc);
+        acc = wt ? fmaf(wt[pair], d, acc) : acc + d;
     }
     if (lane == 0) {
         float * xo = x + (int64_t) t * width + n;
-        *xo = (base == MOE_SET ? 0.f : base == MOE_SCALE ? *xo * xscale[t] : *xo) + acc;
+        *xo = (base == MOE_SET ? 0.f : base == MOE_SCALE ? *xo * xscale[t] : *xo) + acc * out_scale;
     }
 }
 
@@ -265,14 +270,26 @@ __global__ void k_moe_invert(const int32_t * __restrict__ perm, int32_t * __rest
     if (r < n_pairs) row_of[perm[r]] = r;
 }
 __global__ void k_moe_combine(const float * __restrict__ ds, const int32_t * __restrict__ row_of, const float * __restrict__ wt, int top, int width,
-                              float * __restrict__ x, int base, const float * __restrict__ xscale) {
+                              float * __restrict__ x, int base, const float * __restrict__ xscale, float out_scale) {
     const int t = blockIdx.x;
     for (int n = threadIdx.x; n < width; n += blockDim.x) {
         float acc = 0.f;
-        for (int k = 0; k < top; k++) acc = fmaf(wt[(int64_t) t * top + k], ds[(int64_t) row_of[(int64_t) t * top + k] * width + n], acc);
+        for (int k = 0; k < top; k++) {
+            const float d = ds[(int64_t) row_of[(int64_t) t * top + k] * width + n];
+            acc = wt ? fmaf(wt[(int64_t) t * top + k], d, acc) : acc + d;
+        }
         float * xo = x + (int64_t) t * width + n;
-        *xo = (base == MOE_SET ? 0.f : base == MOE_SCALE ? *xo * xscale[t] : *xo) + acc;
+        *xo = (base == MOE_SET ? 0.f : base == MOE_SCALE ? *xo * xscale[t] : *xo) + acc * out_scale;
     }
+}
+
+template <typename OT>
+__global__ void k_silu_mul(const float * __restrict__ gu, OT * __restrict__ y, int n_rows, int ff, const float * __restrict__ in_wt, const int32_t * __restrict__ perm) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t) n_rows * ff) return;
+    const int64_t r = i / ff, j = i - r * ff;
+    const float s = in_wt ? in_wt[perm ? perm[r] : r] : 1.f;
+    put(y, i, silu_f(s * gu[r * 2 * ff + j]) * (s * gu[r * 2 * ff + ff + j]));
 }
 
 template <typename WT> bool vec_ok(const void * a, const void * b, int K) {
@@ -318,35 +335,44 @@ int launch_moe_route_sigmoid(const void * h, int htype, const float * wr, const 
     if (rc) return rc;
     return ck_launch([&] { k_moe_route_sigmoid<float><<<n_tokens, threads, smem, st>>>((const float *) h, wr, correction, p, width, shared_gate, idx, wt, sg_out); });
 }
+int launch_silu_mul(const float * gu, void * y, int otype, int n_rows, int ff, const float * in_wt, const int32_t * perm, cudaStream_t st) {
+    const int64_t n = (int64_t) n_rows * ff;
+    if (n <= 0) return 0;
+    const unsigned grid = (unsigned) ((n + 255) / 256);
+    return ck_launch([&] {
+        if (otype == T_BF16) k_silu_mul<__nv_bfloat16><<<grid, 256, 0, st>>>(gu, (__nv_bfloat16 *) y, n_rows, ff, in_wt, perm);
+        else k_silu_mul<float><<<grid, 256, 0, st>>>(gu, (float *) y, n_rows, ff, in_wt, perm);
+    });
+}
 int launch_moe_gateup_rows(const void * h, int type, const void * gateup, const int32_t * idx, const MoeParams & p, int width, void * y, int n_tokens,
-                           cudaStream_t st) {
+                           cudaStream_t st, const float * in_wt) {
     if (n_tokens <= 0) return 0;
     if (!moe_ok(p)) return (int) cudaErrorInvalidValue;
     const dim3 grid((unsigned) ((p.ff + 7) / 8), (unsigned) (n_tokens * p.top));
     return ck_launch([&] {
         if (type == T_BF16) {
             using B = __nv_bfloat16;
-            if (vec_ok<B>(h, gateup, width)) k_moe_gateup_rows<B, true><<<grid, 256, 0, st>>>((const B *) h, (const B *) gateup, idx, p, width, (B *) y);
-            else k_moe_gateup_rows<B, false><<<grid, 256, 0, st>>>((const B *) h, (const B *) gateup, idx, p, width, (B *) y);
+            if (vec_ok<B>(h, gateup, width)) k_moe_gateup_rows<B, true><<<grid, 256, 0, st>>>((const B *) h, (const B *) gateup, idx, p, width, (B *) y, in_wt);
+            else k_moe_gateup_rows<B, false><<<grid, 256, 0, st>>>((const B *) h, (const B *) gateup, idx, p, width, (B *) y, in_wt);
         } else {
-            if (vec_ok<float>(h, gateup, width)) k_moe_gateup_rows<float, true><<<grid, 256, 0, st>>>((const float *) h, (const float *) gateup, idx, p, width, (float *) y);
-            else k_moe_gateup_rows<float, false><<<grid, 256, 0, st>>>((const float *) h, (const float *) gateup, idx, p, width, (float *) y);
+            if (vec_ok<float>(h, gateup, width)) k_moe_gateup_rows<float, true><<<grid, 256, 0, st>>>((const float *) h, (const float *) gateup, idx, p, width, (float *) y, in_wt);
+            else k_moe_gateup_rows<float, false><<<grid, 256, 0, st>>>((const float *) h, (const float *) gateup, idx, p, width, (float *) y, in_wt);
         }
     });
 }
 int launch_moe_down_rows(const void * y, int type, const void * down, const int32_t * idx, const float * wt, const MoeParams & p, int width, float * x,
-                         int n_tokens, cudaStream_t st, int base, const float * xscale) {
+                         int n_tokens, cudaStream_t st, int base, const float * xscale, float out_scale) {
     if (n_tokens <= 0) return 0;
     if (!moe_ok(p) || (base == MOE_SCALE && !xscale)) return (int) cudaErrorInvalidValue;
     const dim3 grid((unsigned) ((width + 7) / 8), (unsigned) n_tokens);
     return ck_launch([&] {
         if (type == T_BF16) {
             using B = __nv_bfloat16;
-            if (vec_ok<B>(y, down, p.ff)) k_moe_down_rows<B, true><<<grid, 256, 0, st>>>((const B *) y, (const B *) down, idx, wt, p, width, x, base, xscale);
-            else k_moe_down_rows<B, false><<<grid, 256, 0, st>>>((const B *) y, (const B *) down, idx, wt, p, width, x, base, xscale);
+            if (vec_ok<B>(y, down, p.ff)) k_moe_down_rows<B, true><<<grid, 256, 0, st>>>((const B *) y, (const B *) down, idx, wt, p, width, x, base, xscale, out_scale);
+            else k_moe_down_rows<B, false><<<grid, 256, 0, st>>>((const B *) y, (const B *) down, idx, wt, p, width, x, base, xscale, out_scale);
         } else {
-            if (vec_ok<float>(y, down, p.ff)) k_moe_down_rows<float, true><<<grid, 256, 0, st>>>((const float *) y, (const float *) down, idx, wt, p, width, x, base, xscale);
-            else k_moe_down_rows<float, false><<<grid, 256, 0, st>>>((const float *) y, (const float *) down, idx, wt, p, width, x, base, xscale);
+            if (vec_ok<float>(y, down, p.ff)) k_moe_down_rows<float, true><<<grid, 256, 0, st>>>((const float *) y, (const float *) down, idx, wt, p, width, x, base, xscale, out_scale);
+            else k_moe_down_rows<float, false><<<grid, 256, 0, st>>>((const float *) y, (const float *) down, idx, wt, p, width, x, base, xscale, out_scale);
         }
     });
 }
@@ -366,13 +392,13 @@ int launch_moe_gather(const void * h, int type, const int32_t * perm, int top, i
     });
 }
 int launch_moe_combine(const float * ds, const int32_t * perm, int32_t * row_of, const float * wt, int top, int width, float * x, int n_tokens,
-                       cudaStream_t st, int base, const float * xscale) {
+                       cudaStream_t st, int base, const float * xscale, float out_scale) {
     if (n_tokens <= 0) return 0;
     if (base == MOE_SCALE && !xscale) return (int) cudaErrorInvalidValue;
     const int n_pairs = n_tokens * top;
     int rc = ck_launch([&] { k_moe_invert<<<(unsigned) ((n_pairs + 255) / 256), 256, 0, st>>>(perm, row_of, n_pairs); });
     if (rc) return rc;
-    return ck_launch([&] { k_moe_combine<<<n_tokens, 256, 0, st>>>(ds, row_of, wt, top, width, x, base, xscale); });
+    return ck_launch([&] { k_moe_combine<<<n_tokens, 256, 0, st>>>(ds, row_of, wt, top, width, x, base, xscale, out_scale); });
 }
 
 }  // namespace pb

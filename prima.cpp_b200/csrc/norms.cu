@@ -169,19 +169,20 @@ __global__ void __launch_bounds__(256) k_depth_average_norm_shift(const float * 
 
 template <typename OT>
 __global__ void __launch_bounds__(256) k_norm_gate(const float * __restrict__ y, const float * __restrict__ gate, int64_t ldg, int part,
-                                                   const float * __restrict__ w, int gate_act, float eps, OT * __restrict__ out, int inner) {
+                                                   const float * __restrict__ w, int gate_act, float eps, OT * __restrict__ out, int inner, int64_t ldo,
+                                                   float out_scale) {
     __shared__ float red[33];
     const int t = blockIdx.x, grp = blockIdx.y;
     const float * yr = y + (int64_t) t * inner + grp * part;
-    const float * gr = gate + (int64_t) t * ldg + grp * part;
+    const float * gr = gate_act >= 0 ? gate + (int64_t) t * ldg + grp * part : nullptr;
     float q = 0.f;
     for (int i = threadIdx.x; i < part; i += blockDim.x) q = fmaf(yr[i], yr[i], q);
     const float inv = 1.f / sqrtf(block_sum(q, red) / (float) part + eps);
     for (int i = threadIdx.x; i < part; i += blockDim.x) {
         float v = yr[i] * inv;
         if (w) v *= w[grp * part + i];
-        v *= gate_act == 0 ? sigmoid_f(gr[i]) : silu_f(gr[i]);
-        put(out, (int64_t) t * inner + grp * part + i, v);
+        if (gr) v *= gate_act == 0 ? sigmoid_f(gr[i]) : silu_f(gr[i]);
+        put(out, (int64_t) t * ldo + grp * part + i, v * out_scale);
     }
 }
 
@@ -247,13 +248,15 @@ int launch_depth_average_norm_shift(const float * planes, int64_t plane_stride, 
     });
 }
 int launch_norm_gate(const float * y, const float * gate, int64_t ldg, int groups, const float * w, int gate_act, float eps, void * out, int otype,
-                     int n_tokens, int inner, cudaStream_t st) {
+                     int n_tokens, int inner, cudaStream_t st, int64_t ldo, float out_scale) {
     if (n_tokens <= 0) return 0;
     if (groups <= 0 || inner % groups != 0) return (int) cudaErrorInvalidValue;
+    if (!gate) gate_act = -1;
+    if (ldo <= 0) ldo = inner;
     const dim3 grid((unsigned) n_tokens, (unsigned) groups);
     return ck_launch([&] {
-        if (otype == T_BF16) k_norm_gate<__nv_bfloat16><<<grid, 256, 0, st>>>(y, gate, ldg, inner / groups, w, gate_act, eps, (__nv_bfloat16 *) out, inner);
-        else k_norm_gate<float><<<grid, 256, 0, st>>>(y, gate, ldg, inner / groups, w, gate_act, eps, (float *) out, inner);
+        if (otype == T_BF16) k_norm_gate<__nv_bfloat16><<<grid, 256, 0, st>>>(y, gate, ldg, inner / groups, w, gate_act, eps, (__nv_bfloat16 *) out, inner, ldo, out_scale);
+        else k_norm_gate<float><<<grid, 256, 0, st>>>(y, gate, ldg, inner / groups, w, gate_act, eps, (float *) out, inner, ldo, out_scale);
     });
 }
 int launch_clamped_glu(const float * gu, void * y, int otype, int n_tokens, int ff, float limit, cudaStream_t st) {
