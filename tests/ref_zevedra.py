@@ -12,6 +12,10 @@ Two mixers, each two branches side by side over the same input:
                 before a rotate-half partial rotation; a sigmoid gate per output element) + an HGRN2 recurrence;
                 result = (rmsnorm(left) * w_l + rmsnorm(right) * w_r) / 2
 Feed-forward: mixture of SiLU-gated experts, sigmoid router, the chosen scores multiply the experts' INPUT."""
+import json
+import os
+import struct
+
 import numpy as np
 
 
@@ -347,7 +351,7 @@ def from_bf16_bits(b):
     return (b.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
 
 
-def random_weights(cfg, seed=0):
+def random_weights(cfg, seed=0, gain=1.0):
     """Random weights that bfloat16 holds exactly: (bits for the engine, float64 values for the oracle)."""
     rng = np.random.default_rng(seed)
     bits, W = {}, {}
@@ -375,7 +379,7 @@ def random_weights(cfg, seed=0):
         elif leaf == "router":
             a = rng.normal(0, 2.0 / np.sqrt(n_in), shape)
         else:
-            a = rng.normal(0, 1.0 / np.sqrt(n_in), shape)
+            a = rng.normal(0, (gain if name == "head" else 1.0) / np.sqrt(n_in), shape)
         b = to_bf16_bits(np.asarray(a))
         bits[name] = b
         W[name] = from_bf16_bits(b).reshape(shape)
@@ -386,6 +390,26 @@ def set_weight(bits, W, name, value):
     b = to_bf16_bits(np.asarray(value))
     bits[name] = b
     W[name] = from_bf16_bits(b).reshape(np.shape(value))
+
+
+def write_model_dir(path, cfg, bits, shapes=None):
+    """config.json and model.safetensors (an 8-byte header length, a JSON table, then the bfloat16 data)."""
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    shapes = shapes or tensor_shapes(cfg)
+    table, blobs, at = {}, [], 0
+    for name, b in bits.items():
+        raw = np.ascontiguousarray(b).tobytes()
+        table[name] = {"dtype": "BF16", "shape": list(shapes[name]), "data_offsets": [at, at + len(raw)]}
+        at += len(raw)
+        blobs.append(raw)
+    head = json.dumps(table).encode()
+    head += b" " * (-len(head) % 8)
+    with open(os.path.join(path, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(head)))
+        f.write(head)
+        f.write(b"".join(blobs))
 
 
 def rel_err(got, want):
