@@ -404,9 +404,9 @@ def main():
                     "N = 1: one pb200_prefill call, default 512 (llama-bench pp512).  N > 1: only when given — the prompt goes through the layer "
                     "pipeline in 512-token micro-batches (pb200_prefill_stage, NCCL hand-off of the hidden states), e.g. config C5: "
                     "--model qwen2.5-72b --gpus 8 --pp 2048 --n-ctx 4096")
-    ap.add_argument("--arch", default=None, choices=["vamidra", "mumizen", "sapudra"], help="instead of the default workload: prompt / decode throughput of the "
+    ap.add_argument("--arch", default=None, choices=["vamidra", "mumizen", "sapudra", "zevedra"], help="instead of the default workload: prompt / decode throughput of the "
                     "named layer-list design at realistic layer sizes beside its closest existing model at equal size: vamidra beside the Llama "
-                    "graph, mumizen beside vamidra, sapudra beside vamidra and mumizen's experts (prima.cpp_b200/layerlist_bench.py)")
+                    "graph, mumizen beside vamidra, sapudra beside vamidra and mumizen's experts, zevedra beside vamidra and mumizen's recurrence and experts (prima.cpp_b200/layerlist_bench.py)")
     ap.add_argument("--arch-size", default="all", choices=["all", "w2048", "w4096"], help="with --arch: which size")
     ap.add_argument("--ncu", action="store_true", help="bracket the timed region with cudaProfilerStart/Stop (ncu --profile-from-start off)")
     args = ap.parse_args()

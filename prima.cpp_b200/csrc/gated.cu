@@ -41,11 +41,11 @@ __global__ void k_embed_bigram(const WT * __restrict__ table, const WT * __restr
 // grid (tokens, channel tiles): a thread owns one channel of one token
 __global__ void k_causal_conv(const float * __restrict__ u, int64_t ldu, const int32_t * __restrict__ slot, const int32_t * __restrict__ off,
                               const int32_t * __restrict__ entry_of, int channels, int taps, const float * __restrict__ w, int silu_from,
-                              const float * __restrict__ conv_state, int64_t slot_stride, float * __restrict__ out, int64_t ldo) {
+                              float * __restrict__ conv_state, int64_t slot_stride, float * __restrict__ out, int64_t ldo, int advance) {
     const int t = blockIdx.x;
     const int e = entry_of[t];
     const int lt = t - off[e];
-    const float * st = conv_state + (int64_t) slot[e] * slot_stride;   // [taps - 1][channels], row taps - 2 = the input just before this entry
+    float * st = conv_state + (int64_t) slot[e] * slot_stride;   // [taps - 1][channels], row taps - 2 = the input just before this entry
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < channels; c += gridDim.y * blockDim.x) {
         float acc = 0.f;
         for (int d = taps - 1; d >= 0; d--) {                          // oldest input first
@@ -54,6 +54,10 @@ __global__ void k_causal_conv(const float * __restrict__ u, int64_t ldu, const i
             acc = fmaf(w[(int64_t) c * taps + (taps - 1 - d)], in, acc);
         }
         out[(int64_t) t * ldo + c] = c >= silu_from ? silu_f(acc) : acc;
+        if (advance) {   // entries of one token: this thread is the only reader and writer of its channel's state
+            for (int k = 0; k + 1 < taps - 1; k++) st[(int64_t) k * channels + c] = st[(int64_t) (k + 1) * channels + c];
+            if (taps > 1) st[(int64_t) (taps - 2) * channels + c] = u[(int64_t) t * ldu + c];
+        }
     }
 }
 __global__ void k_causal_conv_state(const float * __restrict__ u, int64_t ldu, const int32_t * __restrict__ slot, const int32_t * __restrict__ off, int channels,
@@ -87,11 +91,10 @@ __device__ __forceinline__ void pair_of(int i, int dims, int layout, int & ia, i
 // One CTA per token.  (1) RMS norm over the whole query projection and over the whole key projection with weights; (2) rotation of the
 // leading entries of every query and key head; (3) every head divided by its own root mean square; (4) rotation of the value heads;
 // (5) the K / V rows later tokens can still see go to the cache.  Steps that the design does not have are skipped.
-__global__ void __launch_bounds__(256) k_attn_prep_store(float * __restrict__ q, int64_t ldq, float * __restrict__ k, int64_t ldk, float * __restrict__ v,
-                                                         int64_t ldv, const int32_t * __restrict__ slot, const int32_t * __restrict__ off,
-                                                         const int32_t * __restrict__ pos0, const int32_t * __restrict__ entry_of, AttnParams a, AttnPrep pr,
-                                                         float * __restrict__ kcache, float * __restrict__ vcache, int64_t slot_stride) {
-    __shared__ float red[33];
+__device__ __forceinline__ void attn_prep_token(float * __restrict__ q, int64_t ldq, float * __restrict__ k, int64_t ldk, float * __restrict__ v, int64_t ldv,
+                                                const int32_t * __restrict__ slot, const int32_t * __restrict__ off, const int32_t * __restrict__ pos0,
+                                                const int32_t * __restrict__ entry_of, const AttnParams & a, const AttnPrep & pr, float * __restrict__ kcache,
+                                                float * __restrict__ vcache, int64_t slot_stride, float * red) {
     const int t = blockIdx.x;
     const int e = entry_of[t];
     const int n = off[e + 1] - off[e];
@@ -150,6 +153,13 @@ __global__ void __launch_bounds__(256) k_attn_prep_store(float * __restrict__ q,
     for (int i = threadIdx.x; i < KD; i += blockDim.x) kd[i] = kr[i];
     for (int i = threadIdx.x; i < VD; i += blockDim.x) vd[i] = vr[i];
 }
+__global__ void __launch_bounds__(256) k_attn_prep_store(float * __restrict__ q, int64_t ldq, float * __restrict__ k, int64_t ldk, float * __restrict__ v,
+                                                         int64_t ldv, const int32_t * __restrict__ slot, const int32_t * __restrict__ off,
+                                                         const int32_t * __restrict__ pos0, const int32_t * __restrict__ entry_of, AttnParams a, AttnPrep pr,
+                                                         float * __restrict__ kcache, float * __restrict__ vcache, int64_t slot_stride) {
+    __shared__ float red[33];
+    attn_prep_token(q, ldq, k, ldk, v, ldv, slot, off, pos0, entry_of, a, pr, kcache, vcache, slot_stride, red);
+}
 
 // grid (tokens, heads): one thread per pair of the head's result
 template <typename OT>
@@ -183,10 +193,19 @@ __global__ void k_attn_unrotate_gate(const float * __restrict__ o, const int32_t
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// grid (tokens): warps take the q / k heads (unit vectors), then threads take the per-head numbers
-__global__ void __launch_bounds__(256) k_delta_prep(float * __restrict__ q, int64_t ldq, float * __restrict__ k, int64_t ldk, float * __restrict__ beta,
-                                                    int64_t ldb, float * __restrict__ a, int64_t lda, const float * __restrict__ A_log,
-                                                    const float * __restrict__ dt_bias, int qk_heads, int heads, int dim) {
+// one CTA per token: warps take the q / k heads (unit vectors), then threads take the per-head numbers
+struct RecPrep {
+    int kind = -1;            // 0: gated delta rule (launch_delta_prep), 1: HGRN2 (launch_hgrn2_prep), -1: nothing
+    float * q = nullptr;      int64_t ldq = 0;
+    float * k = nullptr;      int64_t ldk = 0;     // HGRN2: the forget-gate logits
+    float * beta = nullptr;   int64_t ldb = 0;
+    float * a = nullptr;      int64_t lda = 0;
+    const float * p0 = nullptr, * p1 = nullptr;    // A_log, dt_bias  |  f_bias, lower
+    int qk_heads = 0, heads = 0, dim = 0;
+};
+__device__ __forceinline__ void delta_prep_token(float * __restrict__ q, int64_t ldq, float * __restrict__ k, int64_t ldk, float * __restrict__ beta, int64_t ldb,
+                                                 float * __restrict__ a, int64_t lda, const float * __restrict__ A_log, const float * __restrict__ dt_bias,
+                                                 int qk_heads, int heads, int dim) {
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const float qs = 1.f / sqrtf((float) dim);
@@ -206,14 +225,85 @@ __global__ void __launch_bounds__(256) k_delta_prep(float * __restrict__ q, int6
         *ap = expf(-expf(A_log[h]) * sp);
     }
 }
-__global__ void k_hgrn2_prep(float * __restrict__ q, int64_t ldq, float * __restrict__ f, int64_t ldf, const float * __restrict__ f_bias,
-                             const float * __restrict__ lower, int n) {
+__global__ void __launch_bounds__(256) k_delta_prep(float * __restrict__ q, int64_t ldq, float * __restrict__ k, int64_t ldk, float * __restrict__ beta,
+                                                    int64_t ldb, float * __restrict__ a, int64_t lda, const float * __restrict__ A_log,
+                                                    const float * __restrict__ dt_bias, int qk_heads, int heads, int dim) {
+    delta_prep_token(q, ldq, k, ldk, beta, ldb, a, lda, A_log, dt_bias, qk_heads, heads, dim);
+}
+__device__ __forceinline__ void hgrn2_prep_token(float * __restrict__ q, int64_t ldq, float * __restrict__ f, int64_t ldf, const float * __restrict__ f_bias,
+                                                 const float * __restrict__ lower, int n) {
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float * qp = q + (int64_t) t * ldq + i, * fp = f + (int64_t) t * ldf + i;
         *qp = silu_f(*qp);
         const float lo = lower[i];
         *fp = lo + (1.f - lo) * sigmoid_f(*fp + f_bias[i]);
+    }
+}
+__global__ void k_hgrn2_prep(float * __restrict__ q, int64_t ldq, float * __restrict__ f, int64_t ldf, const float * __restrict__ f_bias,
+                             const float * __restrict__ lower, int n) {
+    hgrn2_prep_token(q, ldq, f, ldf, f_bias, lower, n);
+}
+// everything a token's two branches need before their kernels, in one launch: the recurrence's inputs, then the attention inputs and the cache store
+__global__ void __launch_bounds__(256) k_dual_prep_store(RecPrep rc, float * __restrict__ q, int64_t ldq, float * __restrict__ k, int64_t ldk,
+                                                         float * __restrict__ v, int64_t ldv, const int32_t * __restrict__ slot, const int32_t * __restrict__ off,
+                                                         const int32_t * __restrict__ pos0, const int32_t * __restrict__ entry_of, AttnParams a, AttnPrep pr,
+                                                         float * __restrict__ kcache, float * __restrict__ vcache, int64_t slot_stride) {
+    __shared__ float red[33];
+    if (rc.kind == 0) delta_prep_token(rc.q, rc.ldq, rc.k, rc.ldk, rc.beta, rc.ldb, rc.a, rc.lda, rc.p0, rc.p1, rc.qk_heads, rc.heads, rc.dim);
+    else if (rc.kind == 1) hgrn2_prep_token(rc.q, rc.ldq, rc.k, rc.ldk, rc.p0, rc.p1, rc.qk_heads * rc.dim);
+    attn_prep_token(q, ldq, k, ldk, v, ldv, slot, off, pos0, entry_of, a, pr, kcache, vcache, slot_stride, red);
+}
+
+// ---- C: both branches' results into the operand of the one output product.  grid (tokens, left heads + right heads): a CTA of the first
+// kind turns an attention head back and gates it; one of the second kind divides a recurrence head by its root mean square, applies the
+// weight and the gate ----
+template <typename OT>
+__global__ void __launch_bounds__(128) k_dual_post(const float * __restrict__ o, const int32_t * __restrict__ off, const int32_t * __restrict__ pos0,
+                                                   const int32_t * __restrict__ entry_of, int heads, int vdim, int v_layout, const float * __restrict__ v_freq,
+                                                   const float * __restrict__ gate, int64_t ldg, int gate_mode, float left_scale, const float * __restrict__ y,
+                                                   int r_heads, int r_vdim, const float * __restrict__ r_gate, int64_t ldrg, const float * __restrict__ r_w,
+                                                   int r_gate_act, float eps, float right_scale, OT * __restrict__ out, int64_t ldo) {
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    if ((int) blockIdx.y < heads) {
+        const int h = blockIdx.y;
+        const int e = entry_of[t];
+        const float fp = (float) (pos0[e] + (t - off[e]));
+        const float * src = o + ((int64_t) t * heads + h) * vdim;
+        const int hp = vdim / 2;
+        const float gh = gate_mode == 1 ? sigmoid_f(gate[(int64_t) t * ldg + h]) * left_scale : left_scale;
+        for (int i = threadIdx.x; i < hp + (vdim & 1); i += blockDim.x) {
+            if (i == hp) {
+                const float gg = gate_mode == 2 ? sigmoid_f(gate[(int64_t) t * ldg + (int64_t) h * vdim + vdim - 1]) : 1.f;
+                put(out, (int64_t) t * ldo + (int64_t) h * vdim + vdim - 1, src[vdim - 1] * gh * gg);
+                continue;
+            }
+            int ia, ib;
+            pair_of(i, 2 * hp, v_layout, ia, ib);
+            float va = src[ia], vb = src[ib];
+            if (v_freq) turn(va, vb, -fp * v_freq[i]);
+            float ga = gh, gb = gh;
+            if (gate_mode == 2) {
+                ga *= sigmoid_f(gate[(int64_t) t * ldg + (int64_t) h * vdim + ia]);
+                gb *= sigmoid_f(gate[(int64_t) t * ldg + (int64_t) h * vdim + ib]);
+            }
+            put(out, (int64_t) t * ldo + (int64_t) h * vdim + ia, va * ga);
+            put(out, (int64_t) t * ldo + (int64_t) h * vdim + ib, vb * gb);
+        }
+        return;
+    }
+    const int h = blockIdx.y - heads;
+    const float * yr = y + ((int64_t) t * r_heads + h) * r_vdim;
+    const float * gr = r_gate_act >= 0 ? r_gate + (int64_t) t * ldrg + (int64_t) h * r_vdim : nullptr;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < r_vdim; i += blockDim.x) q = fmaf(yr[i], yr[i], q);
+    const float inv = 1.f / sqrtf(block_sum(q, red) / (float) r_vdim + eps);
+    for (int i = threadIdx.x; i < r_vdim; i += blockDim.x) {
+        float v = yr[i] * inv;
+        if (r_w) v *= r_w[h * r_vdim + i];
+        if (gr) v *= r_gate_act == 0 ? sigmoid_f(gr[i]) : silu_f(gr[i]);
+        put(out, (int64_t) t * ldo + (int64_t) heads * vdim + (int64_t) h * r_vdim + i, v * right_scale);
     }
 }
 
@@ -484,11 +574,12 @@ int launch_causal_conv(const float * u, int64_t ldu, const BatchView & b, int ch
     if (b.n_tokens <= 0 || channels <= 0) return 0;
     if (taps < 1 || !w || (taps > 1 && !conv_state)) return (int) cudaErrorInvalidValue;
     const int tiles = b.n_tokens >= 512 ? 1 : std::min((channels + 127) / 128, 32);   // few tokens: a token's channels spread over CTAs
+    const int advance = b.max_n == 1 && taps > 1;   // one-token entries: the same kernel moves the state on
     int rc = ck_launch([&] {
         k_causal_conv<<<dim3((unsigned) b.n_tokens, (unsigned) tiles), 128, 0, st>>>(u, ldu, b.slot, b.off, b.entry_of, channels, taps, w, silu_from, conv_state,
-                                                                                     slot_stride, out, ldo);
+                                                                                     slot_stride, out, ldo, advance);
     });
-    if (rc || taps == 1) return rc;
+    if (rc || taps == 1 || advance) return rc;
     return ck_launch([&] {
         k_causal_conv_state<<<dim3((unsigned) ((channels + 127) / 128), (unsigned) b.n_entries), 128, 0, st>>>(u, ldu, b.slot, b.off, channels, taps, conv_state, slot_stride);
     });
@@ -567,6 +658,40 @@ int launch_gated_linattn(const GatedLinIO & io, const BatchView & b, const Gated
     if (rc) return rc;
     const dim3 grid((unsigned) (p.heads * ((p.vdim + GSCOLS - 1) / GSCOLS)), (unsigned) b.n_entries);
     return ck_launch([&] { k_gated_linattn_smem<<<grid, 256, smem, st>>>(io, b.slot, b.off, p, state, slot_stride, y); });
+}
+
+int launch_dual_prep_store(int rec_kind, float * rq, int64_t ldrq, float * rk, int64_t ldrk, float * beta, int64_t ldb, float * ra, int64_t lda, const float * p0,
+                           const float * p1, int qk_heads, int r_heads, int r_dim, float * q, int64_t ldq, float * k, int64_t ldk, float * v, int64_t ldv,
+                           const BatchView & b, const AttnParams & a, const AttnPrep & pr, float * kcache, float * vcache, int64_t slot_stride, cudaStream_t st) {
+    if (b.n_tokens <= 0) return 0;
+    if (a.heads <= 0 || a.kv_heads <= 0 || a.dim <= 0 || a.vdim <= 0 || pr.rot_dims < 0 || pr.rot_dims > a.dim || (pr.rot_dims & 1) ||
+        (pr.rot_dims > 0 && !pr.rot_freq) || (pr.v_rot && !pr.v_freq) || (pr.norm == QKN_WHOLE_WEIGHT && (!pr.wq || !pr.wk)) || rec_kind < 0 || rec_kind > 1 ||
+        !rq || !rk || !p0 || !p1 || qk_heads <= 0 || r_dim <= 0 || (rec_kind == 0 && (!beta || !ra || r_heads <= 0)))
+        return (int) cudaErrorInvalidValue;
+    RecPrep rc;
+    rc.kind = rec_kind;
+    rc.q = rq; rc.ldq = ldrq; rc.k = rk; rc.ldk = ldrk; rc.beta = beta; rc.ldb = ldb; rc.a = ra; rc.lda = lda;
+    rc.p0 = p0; rc.p1 = p1; rc.qk_heads = qk_heads; rc.heads = r_heads; rc.dim = r_dim;
+    return ck_launch([&] {
+        k_dual_prep_store<<<b.n_tokens, 256, 0, st>>>(rc, q, ldq, k, ldk, v, ldv, b.slot, b.off, b.pos0, b.entry_of, a, pr, kcache, vcache, slot_stride);
+    });
+}
+
+int launch_dual_post(const float * o, const BatchView & b, int heads, int vdim, int v_layout, const float * v_freq, const float * gate, int64_t ldg, int gate_mode,
+                     float left_scale, const float * y, int r_heads, int r_vdim, const float * r_gate, int64_t ldrg, const float * r_w, int r_gate_act, float eps,
+                     float right_scale, void * out, int64_t ldo, int otype, cudaStream_t st) {
+    if (b.n_tokens <= 0) return 0;
+    if (heads <= 0 || vdim <= 0 || r_heads <= 0 || r_vdim <= 0 || (gate_mode != 0 && !gate) || !o || !y) return (int) cudaErrorInvalidValue;
+    if (!r_gate) r_gate_act = -1;
+    const dim3 grid((unsigned) b.n_tokens, (unsigned) (heads + r_heads));
+    return ck_launch([&] {
+        if (otype == T_BF16)
+            k_dual_post<__nv_bfloat16><<<grid, 128, 0, st>>>(o, b.off, b.pos0, b.entry_of, heads, vdim, v_layout, v_freq, gate, ldg, gate_mode, left_scale, y, r_heads,
+                                                            r_vdim, r_gate, ldrg, r_w, r_gate_act, eps, right_scale, (__nv_bfloat16 *) out, ldo);
+        else
+            k_dual_post<float><<<grid, 128, 0, st>>>(o, b.off, b.pos0, b.entry_of, heads, vdim, v_layout, v_freq, gate, ldg, gate_mode, left_scale, y, r_heads, r_vdim,
+                                                    r_gate, ldrg, r_w, r_gate_act, eps, right_scale, (float *) out, ldo);
+    });
 }
 
 int launch_rmsnorm_pair_residual(const float * a, int64_t lda, const float * bb, int64_t ldb, const float * wa, const float * wb, float mult, float eps,

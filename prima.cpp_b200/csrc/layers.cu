@@ -726,8 +726,10 @@ static int zevedra_configure(const Json & cfg, LayerList & ll, std::string & err
                 ll.bigram.buckets = bg->integer("buckets", 0);
                 ll.bigram.mul_prev = bg->integer("mul_prev", 0);
                 ll.bigram.mul_cur = bg->integer("mul_cur", 0);
-                if (ll.bigram.buckets <= 0 || ll.bigram.buckets > (1ll << 30) || ll.bigram.mul_prev < 0 || ll.bigram.mul_cur < 0 ||
-                    ll.bigram.mul_prev > (1ll << 30) || ll.bigram.mul_cur > (1ll << 30)) { err = "bigram sizes"; return PB200_EINVAL; }
+                if (ll.bigram.buckets <= 0 || ll.bigram.buckets > (1ll << 30)) { err = "bigram sizes"; return PB200_EINVAL; }
+                // (a p + b c) mod n with the factors reduced first: the same row, and the products stay inside 64 bits for any factor
+                ll.bigram.mul_prev = (ll.bigram.mul_prev % ll.bigram.buckets + ll.bigram.buckets) % ll.bigram.buckets;
+                ll.bigram.mul_cur = (ll.bigram.mul_cur % ll.bigram.buckets + ll.bigram.buckets) % ll.bigram.buckets;
             }
         }
     }
@@ -1235,8 +1237,10 @@ int ll_finalize(pb200_model * m) {
         off = (off + 3) / 4 * 4;
     }
     ll.slot_floats = std::max<int64_t>(off, 4);
-    if (ll.n_seq <= 0) {   // as many slots as 8 GiB of state hold, between 4 and 256
-        const int64_t fit = (int64_t) (8ll << 30) / (ll.slot_floats * 4);
+    if (ll.n_seq <= 0) {   // as many slots as 8 GiB of state (or a third of the free device memory, if that is more) hold, between 4 and 256
+        size_t mem_free = 0, mem_total = 0;
+        if (cudaMemGetInfo(&mem_free, &mem_total) != cudaSuccess) mem_free = 0;
+        const int64_t fit = std::max<int64_t>(8ll << 30, (int64_t) (mem_free / 3)) / (ll.slot_floats * 4);
         ll.n_seq = (int) std::min<int64_t>(256, std::max<int64_t>(4, fit));
     }
     CK(m->alloc((void **) &ll.state, (size_t) ll.slot_floats * 4 * (size_t) ll.n_seq));
@@ -1575,7 +1579,6 @@ static int mix_dual(pb200_model * m, const BatchView & b, bool prefill, const LR
     const DualMix & d = L.dual;
     const GatedLinParams & rp = d.rp;
     const int C = d.cols, OD = a.heads * a.vdim, RV = rp.heads * rp.vdim;
-    const size_t es = esize(ct);
     // the slot's arena for this run: K rows | V rows | convolution inputs | recurrent state
     float * kc = ll.state + r.state_off, * vc = kc + (int64_t) a.cache_rows * a.kv_heads * a.dim;
     int64_t o = (int64_t) a.cache_rows * a.kv_heads * (a.dim + a.vdim);
@@ -1600,7 +1603,13 @@ static int mix_dual(pb200_model * m, const BatchView & b, bool prefill, const LR
     pr.norm = d.qk_norm; pr.wq = L.q_norm.data; pr.wk = L.k_norm.data; pr.eps = ll.eps;
     pr.rot_dims = d.rot_dims; pr.rot_layout = d.rot_layout; pr.rot_freq = L.rot_freq.data;
     pr.v_rot = d.v_rot; pr.v_layout = d.rot_layout; pr.v_freq = d.v_rot ? L.vrot_freq.data : nullptr;
-    CK(launch_attn_prep_store(src + d.c_q, ld, src + d.c_k, ld, src + d.c_v, ld, b, a, pr, kc, vc, ll.slot_floats, st));
+    // one launch prepares both branches: the recurrence's inputs (unit vectors, gates, decays), then the attention inputs and the cache store
+    if (d.rec == REC_DELTA)
+        CK(launch_dual_prep_store(0, src + d.c_rq, ld, src + d.c_rk, ld, ll.big + d.c_rb, C, ll.big + d.c_ra, C, L.A_log.data, L.dt_bias.data, rp.qk_heads, rp.heads,
+                                  rp.dim, src + d.c_q, ld, src + d.c_k, ld, src + d.c_v, ld, b, a, pr, kc, vc, ll.slot_floats, st));
+    else
+        CK(launch_dual_prep_store(1, src + d.c_rq, ld, src + d.c_rk, ld, nullptr, 0, nullptr, 0, L.f_bias.data, L.f_lower.data, rp.qk_heads, rp.heads, rp.dim,
+                                  src + d.c_q, ld, src + d.c_k, ld, src + d.c_v, ld, b, a, pr, kc, vc, ll.slot_floats, st));
     AttnIO io;
     io.q = src + d.c_q; io.ldq = ld;
     io.k = src + d.c_k; io.ldk = ld;
@@ -1614,30 +1623,29 @@ static int mix_dual(pb200_model * m, const BatchView & b, bool prefill, const LR
     if (prefill) CK(launch_attn_prefill_io(io, b, a, att_out, att_type, st));
     else CK(launch_attn_decode_io(io, b, a, kc, vc, ll.slot_floats, att_out, att_type, st, ll.lat_part));
     const int64_t ldo = sum ? OD + RV : OD;
-    if (post)
-        CK(launch_attn_unrotate_gate(ll.big2, b, a.heads, a.vdim, d.rot_layout, d.v_rot ? L.vrot_freq.data : nullptr, ll.big + d.c_g, C, d.gate_mode,
-                                     sum ? d.left_scale : 1.f, ll.act, ldo, ct, st));
+    if (post && !sum)
+        CK(launch_attn_unrotate_gate(ll.big2, b, a.heads, a.vdim, d.rot_layout, d.v_rot ? L.vrot_freq.data : nullptr, ll.big + d.c_g, C, d.gate_mode, 1.f, ll.act,
+                                     ldo, ct, st));
     // ---- recurrent branch ----
     CAT(CAT_SCAN);
     GatedLinIO gi;
     gi.q = src + d.c_rq; gi.ldq = ld;
     gi.v = src + d.c_rv; gi.ldv = ld;
     if (d.rec == REC_DELTA) {
-        CK(launch_delta_prep(src + d.c_rq, ld, src + d.c_rk, ld, ll.big + d.c_rb, C, ll.big + d.c_ra, C, L.A_log.data, L.dt_bias.data, rp.qk_heads, rp.heads,
-                             rp.dim, T, st));
         gi.k = src + d.c_rk; gi.ldk = ld;
         gi.decay = ll.big + d.c_ra; gi.ldd = C;
         gi.beta = ll.big + d.c_rb; gi.ldb = C;
     } else {
-        CK(launch_hgrn2_prep(src + d.c_rq, ld, src + d.c_rk, ld, L.f_bias.data, L.f_lower.data, rp.qk_heads * rp.dim, T, st));
         gi.decay = src + d.c_rk; gi.ldd = ld;
     }
     CK(launch_gated_linattn(gi, b, rp, rec_state, ll.slot_floats, ll.yssm, st));
     CAT(CAT_NORM);
     if (sum) {
-        // every head by its own root mean square, the weight all heads share, the SiLU gate, the branch's factor -> beside the attention result
-        CK(launch_norm_gate(ll.yssm, d.rec == REC_DELTA ? ll.big + d.c_rg : nullptr, C, rp.heads, L.onorm.data, d.rec == REC_DELTA ? 1 : -1, ll.eps,
-                            (uint8_t *) ll.act + (size_t) OD * es, ct, T, RV, st, ldo, d.right_scale));
+        // attention heads turned back and gated; recurrence heads by their own root mean square, the weight all heads share, the SiLU gate; both
+        // with their branch's factor, side by side as the operand of the one output product
+        CK(launch_dual_post(ll.big2, b, a.heads, a.vdim, d.rot_layout, d.v_rot ? L.vrot_freq.data : nullptr, ll.big + d.c_g, C, d.gate_mode, d.left_scale, ll.yssm,
+                            rp.heads, rp.vdim, d.rec == REC_DELTA ? ll.big + d.c_rg : nullptr, C, L.onorm.data, d.rec == REC_DELTA ? 1 : -1, ll.eps, d.right_scale,
+                            ll.act, ldo, ct, st));
         CAT(CAT_DENSE);
         return launch_dense(ct, ll.act, ldo, L.out.data, ldo, x, W, T, W, (int) ldo, nullptr, x, W, mult, st);
     }

@@ -305,6 +305,17 @@ int launch_attn_prep_store(float * q, int64_t ldq, float * k, int64_t ldk, float
 int launch_attn_unrotate_gate(const float * o, const BatchView & b, int heads, int vdim, int v_layout, const float * v_freq, const float * gate, int64_t ldg,
                               int gate_mode, float out_scale, void * out, int64_t ldo, int otype, cudaStream_t stream);
 
+// the same with the preparation of a recurrent branch's inputs in front, one launch for both branches of a dual mixer: rec_kind 0 =
+// launch_delta_prep(rq, rk, beta, ra, p0 = A_log, p1 = dt_bias), 1 = launch_hgrn2_prep(rq, rk = forget logits, p0 = f_bias, p1 = lower)
+int launch_dual_prep_store(int rec_kind, float * rq, int64_t ldrq, float * rk, int64_t ldrk, float * beta, int64_t ldb, float * ra, int64_t lda, const float * p0,
+                           const float * p1, int qk_heads, int r_heads, int r_dim, float * q, int64_t ldq, float * k, int64_t ldk, float * v, int64_t ldv,
+                           const BatchView & b, const AttnParams & a, const AttnPrep & pr, float * kcache, float * vcache, int64_t slot_stride, cudaStream_t stream);
+// launch_attn_unrotate_gate of the attention result o and launch_norm_gate (one group per head) of the recurrence's result y in one launch:
+// out[t] = [ left_scale * gated, turned-back attention heads | right_scale * normed, weighted, gated recurrence heads ], rows of ldo elements
+int launch_dual_post(const float * o, const BatchView & b, int heads, int vdim, int v_layout, const float * v_freq, const float * gate, int64_t ldg, int gate_mode,
+                     float left_scale, const float * y, int r_heads, int r_vdim, const float * r_gate, int64_t ldrg, const float * r_w, int r_gate_act, float eps,
+                     float right_scale, void * out, int64_t ldo, int otype, cudaStream_t stream);
+
 // ---- gated linear recurrences: a state S [dim][vdim] f32 per (sequence slot, head) with a decay that every token brings ----
 //   decay_per_channel 0: S <- g S (g [T][heads]);  1: S <- diag(f) S (f [T][qk_heads][dim])
 //   delta 0: S <- S + k v^T;   1 (delta rule): u = beta (v - S^T k), S <- S + k u^T (beta [T][heads]), after the decay

@@ -1,7 +1,8 @@
 """Throughput of the layer-list family at sizes that resemble a real model's layers, random weights, beside the closest existing model at
 equal width / feed-forward / head sizes / number of layer runs: Vamidra beside the Llama graph over Q4_K weights (``bench.py --arch
 vamidra``), Mumizen beside Vamidra (``bench.py --arch mumizen``, :func:`run_mumizen`), Sapudra beside Vamidra and, for its experts, Mumizen
-(``bench.py --arch sapudra``, :func:`run_sapudra`).  Prints one JSON line.
+(``bench.py --arch sapudra``, :func:`run_sapudra`), Zevedra beside Vamidra (attention, convolution, plain products) and Mumizen (recurrence,
+experts) (``bench.py --arch zevedra``, :func:`run_zevedra`).  Prints one JSON line.
 
 Per size: prompt tokens/s (one sequence of 512 and 2048 tokens) and decode tokens/s (batch 1 and 8 at a 1024-token context) of both
 models through their public entry points (host token ids in, host logits / greedy tokens out), the device time of a prompt and of a
@@ -66,6 +67,8 @@ def run(args, pkg, lib):
         return run_mumizen(args, pkg, lib)
     if args.arch == "sapudra":
         return run_sapudra(args, pkg, lib)
+    if args.arch == "zevedra":
+        return run_zevedra(args, pkg, lib)
     import numpy as np
     import torch
     hbm, tflops, src = peaks()
@@ -542,6 +545,154 @@ def run_sapudra(args, pkg, lib):
             e[f"decode_b{B}_experts_frac_of_hbm_peak"] = 2.0 * mexpert * B / c[f"decode_b{B}_device_ms"]["experts"] / 1e6 / hbm
             e[f"decode_b{B}_experts_ms"] = c[f"decode_b{B}_device_ms"]["experts"]
         out["mumizen_experts"] = e
+        res["sizes"][key] = out
+        torch.cuda.empty_cache()
+    res["gpu_launches"] = int(lib.c.pb200_kernel_launches())
+    print(json.dumps(res))
+    return res
+
+
+# ---------------------------------------------------------------------------------------------------------------
+ZEVEDRA_SIZES = {
+    "w2048": dict(r_heads=16, r_kv=4, r_dim=128, r_vdim=128, conv=4, experts=16, top=2, expert_ff=2048),
+    "w4096": dict(r_heads=32, r_kv=8, r_dim=128, r_vdim=128, conv=4, experts=16, top=2, expert_ff=4096),
+}
+
+
+def zevedra_config(s, z):
+    """Four layers, the first two run twice (six layer runs): sink attention beside HGRN2, then windowed attention beside the gated delta
+    rule, at the width / head sizes / window of SIZES; every layer has a mixture of experts."""
+    H, G, D = s["heads"], s["kv_heads"], s["dim"]
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    p2 = {"type": "parallel_2", "mlp": moe,
+          "mixer": {"left": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "rot": {"base": 100000.0, "dims": D // 2}},
+                    "right": {"heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"]}}}
+    p1 = {"type": "parallel", "mlp": moe,
+          "mixer": {"left": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "conv": z["conv"], "mask": {"size": s["window"]},
+                             "rot": {"base": 1000000.0, "dims": D}},
+                    "right": {"heads": z["r_heads"], "kv_heads": z["r_kv"], "dim": z["r_dim"], "vdim": z["r_vdim"], "conv": z["conv"]},
+                    "left_scale": 0.5, "right_scale": 0.8}}
+    return {"architecture": "Zevedra", "width": s["width"], "vocab": s["vocab"], "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "embedding": {"scale": s["width"] ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 131, "mul_cur": 17}},
+            "layers": [p2, p1, dict(p2), dict(p1)], "loop": {"start": 0, "stop": 2, "times": 2}}
+
+
+def zevedra_products(cfg):
+    """((N, K) of the plain dense products, expert weight elements touched, convolution channels) of one token through all six layer runs."""
+    W, out, expert, conv = cfg["width"], [], 0, 0
+    for li in (0, 1, 0, 1, 2, 3):
+        l = cfg["layers"][li]
+        a, r = l["mixer"]["left"], l["mixer"]["right"]
+        qkv = a["heads"] * a["dim"] + a["kv_heads"] * (a["dim"] + a["vdim"])
+        OD, RV = a["heads"] * a["vdim"], r["heads"] * r["vdim"]
+        if l["type"] == "parallel":
+            RQ = r["kv_heads"] * r["dim"]
+            out += [(qkv + a["heads"] + 2 * RQ + 2 * RV + 2 * r["heads"], W), (W, OD + RV)]
+            conv += qkv + 2 * RQ + RV
+        else:
+            out += [(qkv + OD + 2 * r["heads"] * r["dim"] + RV, W), (W, OD), (W, RV)]
+        expert += l["mlp"]["router"]["top"] * 3 * l["mlp"]["expert"]["ff"] * W
+    return out, expert, conv
+
+
+def run_zevedra(args, pkg, lib):
+    """Zevedra beside Vamidra (attention, short convolution, plain products, norms: the same or like kernels) and beside Mumizen (its
+    fixed-decay recurrence is the like kernel of the gated recurrences; its experts) at equal width / head size / expert size and six
+    layer runs each: whole-model prompt and decode throughput through the public entry points, device time per kernel category, and for
+    every pair of like kernels the distance from its roofline."""
+    import numpy as np
+    import torch
+    hbm, tflops, src = peaks()
+    res = {"metric": "Zevedra prompt / decode throughput beside Vamidra and Mumizen at equal size", "impl": "b200", "arch": "Zevedra", "n_gpus": 1,
+           "dtype": "bf16", "data": "synthetic random weights", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": src}, "sizes": {}}
+    rng = np.random.default_rng(0)
+    CTX = 1024
+
+    def model(cfg):
+        m = pkg.Model.from_config(cfg, dtype="bfloat16", n_ctx=4096, n_seq=16)
+        m.synth(0, 7)
+        m.finalize()
+        return m
+
+    for key in ([args.arch_size] if args.arch_size != "all" else list(SIZES)):
+        s, z = SIZES[key], ZEVEDRA_SIZES[key]
+        W, V, H, G, D = s["width"], s["vocab"], s["heads"], s["kv_heads"], s["dim"]
+        out = {"config": dict(z, width=W, heads=H, kv_heads=G, dim=D, window=s["window"], vocab=V), "layers": 6}
+        # ---------------- the new design ----------------
+        cfg = zevedra_config(s, z)
+        m = model(cfg)
+        a = measure(m, V, args, rng, CTX)
+        m.close()
+        prods, expert, conv_ch = zevedra_products(cfg)
+        rec = 6 * z["r_heads"] * z["r_dim"] * z["r_vdim"]          # state entries a token updates, all runs
+        for T in (512, 2048):
+            pm = a[f"prompt{T}_device_ms"]
+            a[f"prompt{T}_dense_frac_of_tensor_peak"] = 2.0 * sum(n * k for n, k in prods) * T / pm["dense"] / 1e9 / tflops
+            a[f"prompt{T}_experts_frac_of_tensor_peak"] = 2.0 * expert * T / pm["experts"] / 1e9 / tflops
+            vis = 3 * sum(min(i + 1, s["window"]) for i in range(T)) + 3 * T * (T + 1) // 2     # three windowed and three causal runs
+            a[f"prompt{T}_attention_tflops"] = 4.0 * D * H * vis / pm["attention"] / 1e9
+            a[f"prompt{T}_scan_state_updates_per_ns"] = rec * T / pm["scan"] / 1e6
+            a[f"prompt{T}_conv_gbs"] = conv_ch * T * 8.0 / pm["conv"] / 1e6                     # inputs read, outputs written (fp32)
+            # three windowed runs: two norms (x read, operand written), both branches' results read in fp32 with the gate and written as operand;
+            # three sink runs: a norm, the recurrence's result normed, two products normed and joined onto the stream with the next norm
+            OD, RV = H * D, z["r_heads"] * z["r_vdim"]
+            a[f"prompt{T}_norm_gbs"] = T * (3 * (12.0 * W + 6.0 * OD + 10.0 * RV) + 3 * (6.0 * W + 6.0 * RV + 18.0 * W)) / pm["norm"] / 1e6
+        wb = 2.0 * sum(n * k for n, k in prods)
+        a["weight_bytes_per_token"] = wb + 2.0 * expert + 2.0 * V * W
+        rows = 3 * min(CTX, s["window"]) + 3 * CTX
+        for B in (1, 8):
+            pm = a[f"decode_b{B}_device_ms"]
+            a[f"decode_b{B}_dense_frac_of_hbm_peak"] = wb / pm["dense"] / 1e6 / hbm
+            a[f"decode_b{B}_experts_frac_of_hbm_peak"] = 2.0 * expert * B / pm["experts"] / 1e6 / hbm
+            a[f"decode_b{B}_attention_gbs"] = B * rows * G * 2 * D * 4.0 / pm["attention"] / 1e6
+            a[f"decode_b{B}_scan_gbs"] = B * rec * 8.0 / pm["scan"] / 1e6                       # the state read and written
+            a[f"decode_b{B}_whole_step_frac_of_hbm_peak"] = a["weight_bytes_per_token"] / a[f"decode_b{B}_ms_per_step"] / 1e6 / hbm
+        out["zevedra"] = a
+        # ---------------- Vamidra: windowed attention, convolution + scan, plain products, norms ----------------
+        vcfg = vamidra_config(s)
+        m = model(vcfg)
+        b = measure(m, V, args, rng, CTX)
+        m.close()
+        shapes = dense_shapes(s, vcfg)
+        vconv = 3 * (s["ssm_heads"] * s["vdim"] + 2 * s["groups"] * s["state"])
+        vrec = 3 * s["ssm_heads"] * s["state"] * s["vdim"]
+        for T in (512, 2048):
+            pm = b[f"prompt{T}_device_ms"]
+            b[f"prompt{T}_dense_frac_of_tensor_peak"] = 2.0 * sum(n * k for n, k in shapes) * T / pm["dense"] / 1e9 / tflops
+            vis = sum(min(i + 1, s["window"]) + max(0, min(s["keep_first"], i + 1 - s["window"])) for i in range(T))
+            b[f"prompt{T}_attention_tflops"] = 3 * 4.0 * D * H * vis / pm["attention"] / 1e9
+            b[f"prompt{T}_scan_state_updates_per_ns"] = vrec * T / pm["scan"] / 1e6
+            b[f"prompt{T}_conv_gbs"] = vconv * T * 8.0 / pm["conv"] / 1e6
+            b[f"prompt{T}_norm_gbs"] = (12 * T * W * 6.0 + 3 * T * s["ssm_heads"] * s["vdim"] * 10.0) / pm["norm"] / 1e6
+        wbv = 2.0 * sum(n * k for n, k in shapes)
+        b["weight_bytes_per_token"] = wbv + 2.0 * V * W
+        vrows = min(CTX, s["window"] + s["keep_first"])
+        for B in (1, 8):
+            pm = b[f"decode_b{B}_device_ms"]
+            b[f"decode_b{B}_dense_frac_of_hbm_peak"] = wbv / pm["dense"] / 1e6 / hbm
+            b[f"decode_b{B}_attention_gbs"] = 3 * B * vrows * G * 2 * D * 4.0 / pm["attention"] / 1e6
+            b[f"decode_b{B}_scan_gbs"] = B * vrec * 8.0 / pm["scan"] / 1e6
+            b[f"decode_b{B}_whole_step_frac_of_hbm_peak"] = b["weight_bytes_per_token"] / b[f"decode_b{B}_ms_per_step"] / 1e6 / hbm
+        out["vamidra"] = b
+        # ---------------- Mumizen: the fixed-decay recurrence and the experts at equal sizes ----------------
+        mz = dict(MUMIZEN_SIZES[key], experts=z["experts"], top=z["top"], expert_ff=z["expert_ff"])
+        mcfg = mumizen_config(s, mz)
+        m = model(mcfg)
+        c = measure(m, V, args, rng, CTX)
+        m.close()
+        _, mexpert = mumizen_products(mcfg, True)
+        n_lin = sum(l["type"] != "latent_attention" for l in mcfg["layers"])
+        mrec = n_lin * mz["heads"] * mz["dim"] * mz["vdim"]
+        e = {}
+        for T in (512, 2048):
+            pm = c[f"prompt{T}_device_ms"]
+            e[f"prompt{T}_experts_frac_of_tensor_peak"] = 2.0 * mexpert * T / pm["experts"] / 1e9 / tflops
+            e[f"prompt{T}_scan_state_updates_per_ns"] = mrec * T / pm["scan"] / 1e6
+        for B in (1, 8):
+            pm = c[f"decode_b{B}_device_ms"]
+            e[f"decode_b{B}_experts_frac_of_hbm_peak"] = 2.0 * mexpert * B / pm["experts"] / 1e6 / hbm
+            e[f"decode_b{B}_scan_gbs"] = B * mrec * 8.0 / pm["scan"] / 1e6
+        out["mumizen_like_kernels"] = e
         res["sizes"][key] = out
         torch.cuda.empty_cache()
     res["gpu_launches"] = int(lib.c.pb200_kernel_launches())
