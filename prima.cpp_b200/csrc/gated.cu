@@ -308,7 +308,7 @@ __global__ void __launch_bounds__(128) k_dual_post(const float * __restrict__ o,
 }
 
 // A CTA owns one head and 16 value columns.  LN lanes share a column: thread (pl = tid / LN, ng = tid % LN) keeps S[n][column pl] for
-// n = ng, ng + LN, ... (NREG values).  Tokens are walked in chunks of 16 whose q, k (or per-channel decay) rows, v columns and per-head
+// n = NREG ng .. NREG ng + NREG - 1 (consecutive, so that a token's k and q entries come out of shared memory as 16-byte loads).  Tokens are walked in chunks of 16 whose q, k (or per-channel decay) rows, v columns and per-head
 // numbers go through registers into shared memory; the loads of the next chunk are in flight while the current one runs.  A token costs a
 // thread NREG fused steps and the column ONE shuffle reduction: for the delta rule the products of the OLD state with k and with q are
 // reduced together (with k . q), and  u = beta (v - g S_old^T k),  y = g S_old^T q + u (k . q)  follow without a second pass.
@@ -334,10 +334,28 @@ __global__ void __launch_bounds__(GCOLS * LN) k_gated_linattn_reg(GatedLinIO io,
     float S[NREG];
 #pragma unroll
     for (int j = 0; j < NREG; j++) {
-        const int nn = ng + LN * j;
+        const int nn = ng * NREG + j;
         S[j] = (pok && nn < N) ? gst[(int64_t) nn * P + pcol] : 0.f;
     }
     const int t0 = off[e], n = off[e + 1] - t0;
+    const bool vec4 = NREG % 4 == 0 && (N & 3) == 0;
+    // this thread's NREG entries of a staged row (zeros beyond the key size)
+    auto row_regs = [&](const float * row, float (&r)[NREG]) {
+        if (vec4) {
+#pragma unroll
+            for (int j = 0; j < NREG; j += 4) {
+                const int nn = ng * NREG + j;
+                const float4 v = nn < N ? *reinterpret_cast<const float4 *>(row + nn) : make_float4(0.f, 0.f, 0.f, 0.f);
+                r[j] = v.x; r[(j + 1) % NREG] = v.y; r[(j + 2) % NREG] = v.z; r[(j + 3) % NREG] = v.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < NREG; j++) {
+                const int nn = ng * NREG + j;
+                r[j] = nn < N ? row[nn] : 0.f;
+            }
+        }
+    };
     float rk[NREG], rq[NREG], rv[NV], rg = 0.f;
     auto fetch = [&](int c0) {
         const int nc = min(GCHUNK, n - c0);
@@ -382,20 +400,18 @@ __global__ void __launch_bounds__(GCOLS * LN) k_gated_linattn_reg(GatedLinIO io,
         if (c0 + GCHUNK < n) fetch(c0 + GCHUNK);
         for (int tt = 0; tt < nc; tt++) {
             const float xv = Vs[tt * GCOLS + pl];
-            const float * Kr = Ks + tt * N, * Qr = Qs + tt * N;
+            float kk[NREG], qq[NREG];
+            row_regs(Ks + tt * N, kk);
+            row_regs(Qs + tt * N, qq);
             float out;
             if constexpr (DELTA) {
-                // old state against k and q, and k . q, in one reduction
+                // old state against k and q, and k . q, in one reduction (entries beyond the key size are zero on both sides)
                 float sk = 0.f, sq = 0.f, kq = 0.f;
 #pragma unroll
                 for (int j = 0; j < NREG; j++) {
-                    const int nn = ng + LN * j;
-                    if (nn < N) {
-                        const float kk = Kr[nn], qq = Qr[nn];
-                        sk = fmaf(S[j], kk, sk);
-                        sq = fmaf(S[j], qq, sq);
-                        kq = fmaf(kk, qq, kq);
-                    }
+                    sk = fmaf(S[j], kk[j], sk);
+                    sq = fmaf(S[j], qq[j], sq);
+                    kq = fmaf(kk[j], qq[j], kq);
                 }
 #pragma unroll
                 for (int o = 1; o < LN; o <<= 1) {
@@ -405,21 +421,15 @@ __global__ void __launch_bounds__(GCOLS * LN) k_gated_linattn_reg(GatedLinIO io,
                 }
                 const float g = Gs[tt], u = Gs[GCHUNK + tt] * (xv - g * sk);
 #pragma unroll
-                for (int j = 0; j < NREG; j++) {
-                    const int nn = ng + LN * j;
-                    if (nn < N) S[j] = fmaf(Kr[nn], u, g * S[j]);
-                }
+                for (int j = 0; j < NREG; j++) S[j] = fmaf(kk[j], u, g * S[j]);
                 out = fmaf(u, kq, g * sq);
             } else {
                 float acc = 0.f;
 #pragma unroll
                 for (int j = 0; j < NREG; j++) {
-                    const int nn = ng + LN * j;
-                    if (nn < N) {
-                        if constexpr (CHAN) { const float f = Kr[nn]; S[j] = fmaf(f, S[j], (1.f - f) * xv); }   // key tied to the decay
-                        else S[j] = fmaf(Gs[tt], S[j], Kr[nn] * xv);
-                        acc = fmaf(S[j], Qr[nn], acc);
-                    }
+                    if constexpr (CHAN) S[j] = fmaf(kk[j], S[j], (1.f - kk[j]) * xv);   // key tied to the decay
+                    else S[j] = fmaf(Gs[tt], S[j], kk[j] * xv);
+                    acc = fmaf(S[j], qq[j], acc);                                      // q is zero beyond the key size
                 }
 #pragma unroll
                 for (int o = 1; o < LN; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -430,7 +440,7 @@ __global__ void __launch_bounds__(GCOLS * LN) k_gated_linattn_reg(GatedLinIO io,
     }
 #pragma unroll
     for (int j = 0; j < NREG; j++) {
-        const int nn = ng + LN * j;
+        const int nn = ng * NREG + j;
         if (pok && nn < N) gst[(int64_t) nn * P + pcol] = S[j];
     }
 }
