@@ -91,17 +91,9 @@ __device__ __forceinline__ void pair_of(int i, int dims, int layout, int & ia, i
 // One CTA per token.  (1) RMS norm over the whole query projection and over the whole key projection with weights; (2) rotation of the
 // leading entries of every query and key head; (3) every head divided by its own root mean square; (4) rotation of the value heads;
 // (5) the K / V rows later tokens can still see go to the cache.  Steps that the design does not have are skipped.
-__device__ __forceinline__ void attn_prep_token(float * __restrict__ q, int64_t ldq, float * __restrict__ k, int64_t ldk, float * __restrict__ v, int64_t ldv,
-                                                const int32_t * __restrict__ slot, const int32_t * __restrict__ off, const int32_t * __restrict__ pos0,
-                                                const int32_t * __restrict__ entry_of, const AttnParams & a, const AttnPrep & pr, float * __restrict__ kcache,
-                                                float * __restrict__ vcache, int64_t slot_stride, float * red) {
-    const int t = blockIdx.x;
-    const int e = entry_of[t];
-    const int n = off[e + 1] - off[e];
-    const int p = pos0[e] + (t - off[e]), pend = pos0[e] + n;
+__device__ __forceinline__ void attn_prep_rows(float * qr, float * kr, float * vr, float fp, const AttnParams & a, const AttnPrep & pr, float * red) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    const int QD = a.heads * a.dim, KD = a.kv_heads * a.dim, VD = a.kv_heads * a.vdim;
-    float * qr = q + (int64_t) t * ldq, * kr = k + (int64_t) t * ldk, * vr = v + (int64_t) t * ldv;
+    const int QD = a.heads * a.dim, KD = a.kv_heads * a.dim;
     if (pr.norm == QKN_WHOLE_WEIGHT) {
         float sq = 0.f, sk = 0.f;
         for (int i = threadIdx.x; i < QD; i += blockDim.x) sq = fmaf(qr[i], qr[i], sq);
@@ -112,7 +104,6 @@ __device__ __forceinline__ void attn_prep_token(float * __restrict__ q, int64_t 
         for (int i = threadIdx.x; i < KD; i += blockDim.x) kr[i] = kr[i] * ik * pr.wk[i];
         __syncthreads();
     }
-    const float fp = (float) p;
     if (pr.rot_dims > 1) {
         const int hp = pr.rot_dims / 2, total = (a.heads + a.kv_heads) * hp;
         for (int j = threadIdx.x; j < total; j += blockDim.x) {
@@ -143,7 +134,79 @@ __device__ __forceinline__ void attn_prep_token(float * __restrict__ q, int64_t 
             turn(hv[ia], hv[ib], fp * pr.v_freq[i]);
         }
     }
+}
+// the inputs of a recurrent branch that ride along in the same launch (launch_dual_prep_store)
+struct RecPrep {
+    int kind = -1;            // 0: gated delta rule (launch_delta_prep), 1: HGRN2 (launch_hgrn2_prep), -1: nothing
+    float * q = nullptr;      int64_t ldq = 0;
+    float * k = nullptr;      int64_t ldk = 0;     // HGRN2: the forget-gate logits
+    float * beta = nullptr;   int64_t ldb = 0;
+    float * a = nullptr;      int64_t lda = 0;
+    const float * p0 = nullptr, * p1 = nullptr;    // A_log, dt_bias  |  f_bias, lower
+    int qk_heads = 0, heads = 0, dim = 0;
+};
+__device__ __forceinline__ void delta_prep_rows(float * qr, float * kr, float * bp, float * ap, const float * __restrict__ A_log,
+                                                const float * __restrict__ dt_bias, int qk_heads, int heads, int dim) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const float qs = 1.f / sqrtf((float) dim);
+    for (int hh = warp; hh < 2 * qk_heads; hh += nw) {
+        const bool isq = hh < qk_heads;
+        float * hv = isq ? qr + (int64_t) hh * dim : kr + (int64_t) (hh - qk_heads) * dim;
+        float ss = 0.f;
+        for (int i = lane; i < dim; i += 32) ss = fmaf(hv[i], hv[i], ss);
+        const float inv = (1.f / sqrtf(wsum(ss) + 1e-6f)) * (isq ? qs : 1.f);
+        for (int i = lane; i < dim; i += 32) hv[i] *= inv;
+    }
+    for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+        bp[h] = sigmoid_f(bp[h]);
+        const float z = ap[h] + dt_bias[h];
+        const float sp = z > 20.f ? z : log1pf(expf(z));
+        ap[h] = expf(-expf(A_log[h]) * sp);
+    }
+}
+__device__ __forceinline__ void hgrn2_prep_rows(float * qr, float * fr, const float * __restrict__ f_bias, const float * __restrict__ lower, int n) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        qr[i] = silu_f(qr[i]);
+        const float lo = lower[i];
+        fr[i] = lo + (1.f - lo) * sigmoid_f(fr[i] + f_bias[i]);
+    }
+}
+
+// One CTA per token prepares everything the token's branches need before their kernels.  With `staged` the token's q, k, v rows (and the
+// recurrence's q and k rows) are copied into shared memory once, every step runs there, and the rows go back to global memory (and the
+// K / V rows later tokens can still see to the cache) once: two passes over global memory instead of one per step.
+__global__ void __launch_bounds__(256) k_dual_prep_store(RecPrep rc, float * __restrict__ q, int64_t ldq, float * __restrict__ k, int64_t ldk,
+                                                         float * __restrict__ v, int64_t ldv, const int32_t * __restrict__ slot, const int32_t * __restrict__ off,
+                                                         const int32_t * __restrict__ pos0, const int32_t * __restrict__ entry_of, AttnParams a, AttnPrep pr,
+                                                         float * __restrict__ kcache, float * __restrict__ vcache, int64_t slot_stride, int staged) {
+    extern __shared__ float sm[];
+    __shared__ float red[33];
+    const int t = blockIdx.x;
+    const int e = entry_of[t];
+    const int n = off[e + 1] - off[e];
+    const int p = pos0[e] + (t - off[e]), pend = pos0[e] + n;
+    const int QD = a.heads * a.dim, KD = a.kv_heads * a.dim, VD = a.kv_heads * a.vdim, RQ = rc.kind >= 0 ? rc.qk_heads * rc.dim : 0;
+    float * gq = q + (int64_t) t * ldq, * gk = k + (int64_t) t * ldk, * gv = v + (int64_t) t * ldv;
+    float * grq = rc.kind >= 0 ? rc.q + (int64_t) t * rc.ldq : nullptr, * grk = rc.kind >= 0 ? rc.k + (int64_t) t * rc.ldk : nullptr;
+    float * qr = gq, * kr = gk, * vr = gv, * rqr = grq, * rkr = grk;
+    if (staged) {
+        qr = sm; kr = qr + QD; vr = kr + KD; rqr = vr + VD; rkr = rqr + RQ;
+        for (int i = threadIdx.x; i < QD; i += blockDim.x) qr[i] = gq[i];
+        for (int i = threadIdx.x; i < KD; i += blockDim.x) kr[i] = gk[i];
+        for (int i = threadIdx.x; i < VD; i += blockDim.x) vr[i] = gv[i];
+        for (int i = threadIdx.x; i < RQ; i += blockDim.x) { rqr[i] = grq[i]; rkr[i] = grk[i]; }
+        __syncthreads();
+    }
+    if (rc.kind == 0) delta_prep_rows(rqr, rkr, rc.beta + (int64_t) t * rc.ldb, rc.a + (int64_t) t * rc.lda, rc.p0, rc.p1, rc.qk_heads, rc.heads, rc.dim);
+    else if (rc.kind == 1) hgrn2_prep_rows(rqr, rkr, rc.p0, rc.p1, RQ);
+    attn_prep_rows(qr, kr, vr, (float) p, a, pr, red);
     __syncthreads();
+    if (staged) {
+        for (int i = threadIdx.x; i < QD; i += blockDim.x) gq[i] = qr[i];
+        for (int i = threadIdx.x; i < KD; i += blockDim.x) gk[i] = kr[i];
+        for (int i = threadIdx.x; i < VD; i += blockDim.x) gv[i] = vr[i];
+        for (int i = threadIdx.x; i < RQ; i += blockDim.x) { grq[i] = rqr[i]; grk[i] = rkr[i]; }
+    }
     const int keep = min(a.keep_first, a.cache_rows), ring = a.cache_rows - keep;
     // of the positions that share a ring row only the last one of this entry is stored
     if (p >= keep && (ring <= 0 || p < pend - ring)) return;
@@ -152,13 +215,6 @@ __device__ __forceinline__ void attn_prep_token(float * __restrict__ q, int64_t 
     float * vd = vcache + (int64_t) slot[e] * slot_stride + (int64_t) crow * VD;
     for (int i = threadIdx.x; i < KD; i += blockDim.x) kd[i] = kr[i];
     for (int i = threadIdx.x; i < VD; i += blockDim.x) vd[i] = vr[i];
-}
-__global__ void __launch_bounds__(256) k_attn_prep_store(float * __restrict__ q, int64_t ldq, float * __restrict__ k, int64_t ldk, float * __restrict__ v,
-                                                         int64_t ldv, const int32_t * __restrict__ slot, const int32_t * __restrict__ off,
-                                                         const int32_t * __restrict__ pos0, const int32_t * __restrict__ entry_of, AttnParams a, AttnPrep pr,
-                                                         float * __restrict__ kcache, float * __restrict__ vcache, int64_t slot_stride) {
-    __shared__ float red[33];
-    attn_prep_token(q, ldq, k, ldk, v, ldv, slot, off, pos0, entry_of, a, pr, kcache, vcache, slot_stride, red);
 }
 
 // grid (tokens, heads): one thread per pair of the head's result
@@ -193,66 +249,17 @@ __global__ void k_attn_unrotate_gate(const float * __restrict__ o, const int32_t
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// one CTA per token: warps take the q / k heads (unit vectors), then threads take the per-head numbers
-struct RecPrep {
-    int kind = -1;            // 0: gated delta rule (launch_delta_prep), 1: HGRN2 (launch_hgrn2_prep), -1: nothing
-    float * q = nullptr;      int64_t ldq = 0;
-    float * k = nullptr;      int64_t ldk = 0;     // HGRN2: the forget-gate logits
-    float * beta = nullptr;   int64_t ldb = 0;
-    float * a = nullptr;      int64_t lda = 0;
-    const float * p0 = nullptr, * p1 = nullptr;    // A_log, dt_bias  |  f_bias, lower
-    int qk_heads = 0, heads = 0, dim = 0;
-};
-__device__ __forceinline__ void delta_prep_token(float * __restrict__ q, int64_t ldq, float * __restrict__ k, int64_t ldk, float * __restrict__ beta, int64_t ldb,
-                                                 float * __restrict__ a, int64_t lda, const float * __restrict__ A_log, const float * __restrict__ dt_bias,
-                                                 int qk_heads, int heads, int dim) {
-    const int t = blockIdx.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    const float qs = 1.f / sqrtf((float) dim);
-    for (int hh = warp; hh < 2 * qk_heads; hh += nw) {
-        const bool isq = hh < qk_heads;
-        float * hv = isq ? q + (int64_t) t * ldq + (int64_t) hh * dim : k + (int64_t) t * ldk + (int64_t) (hh - qk_heads) * dim;
-        float ss = 0.f;
-        for (int i = lane; i < dim; i += 32) ss = fmaf(hv[i], hv[i], ss);
-        const float inv = (1.f / sqrtf(wsum(ss) + 1e-6f)) * (isq ? qs : 1.f);
-        for (int i = lane; i < dim; i += 32) hv[i] *= inv;
-    }
-    for (int h = threadIdx.x; h < heads; h += blockDim.x) {
-        float * bp = beta + (int64_t) t * ldb + h, * ap = a + (int64_t) t * lda + h;
-        *bp = sigmoid_f(*bp);
-        const float z = *ap + dt_bias[h];
-        const float sp = z > 20.f ? z : log1pf(expf(z));
-        *ap = expf(-expf(A_log[h]) * sp);
-    }
-}
+// the two preparations as kernels of their own (one CTA per token)
 __global__ void __launch_bounds__(256) k_delta_prep(float * __restrict__ q, int64_t ldq, float * __restrict__ k, int64_t ldk, float * __restrict__ beta,
                                                     int64_t ldb, float * __restrict__ a, int64_t lda, const float * __restrict__ A_log,
                                                     const float * __restrict__ dt_bias, int qk_heads, int heads, int dim) {
-    delta_prep_token(q, ldq, k, ldk, beta, ldb, a, lda, A_log, dt_bias, qk_heads, heads, dim);
-}
-__device__ __forceinline__ void hgrn2_prep_token(float * __restrict__ q, int64_t ldq, float * __restrict__ f, int64_t ldf, const float * __restrict__ f_bias,
-                                                 const float * __restrict__ lower, int n) {
-    const int t = blockIdx.x;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        float * qp = q + (int64_t) t * ldq + i, * fp = f + (int64_t) t * ldf + i;
-        *qp = silu_f(*qp);
-        const float lo = lower[i];
-        *fp = lo + (1.f - lo) * sigmoid_f(*fp + f_bias[i]);
-    }
+    const int64_t t = blockIdx.x;
+    delta_prep_rows(q + t * ldq, k + t * ldk, beta + t * ldb, a + t * lda, A_log, dt_bias, qk_heads, heads, dim);
 }
 __global__ void k_hgrn2_prep(float * __restrict__ q, int64_t ldq, float * __restrict__ f, int64_t ldf, const float * __restrict__ f_bias,
                              const float * __restrict__ lower, int n) {
-    hgrn2_prep_token(q, ldq, f, ldf, f_bias, lower, n);
-}
-// everything a token's two branches need before their kernels, in one launch: the recurrence's inputs, then the attention inputs and the cache store
-__global__ void __launch_bounds__(256) k_dual_prep_store(RecPrep rc, float * __restrict__ q, int64_t ldq, float * __restrict__ k, int64_t ldk,
-                                                         float * __restrict__ v, int64_t ldv, const int32_t * __restrict__ slot, const int32_t * __restrict__ off,
-                                                         const int32_t * __restrict__ pos0, const int32_t * __restrict__ entry_of, AttnParams a, AttnPrep pr,
-                                                         float * __restrict__ kcache, float * __restrict__ vcache, int64_t slot_stride) {
-    __shared__ float red[33];
-    if (rc.kind == 0) delta_prep_token(rc.q, rc.ldq, rc.k, rc.ldk, rc.beta, rc.ldb, rc.a, rc.lda, rc.p0, rc.p1, rc.qk_heads, rc.heads, rc.dim);
-    else if (rc.kind == 1) hgrn2_prep_token(rc.q, rc.ldq, rc.k, rc.ldk, rc.p0, rc.p1, rc.qk_heads * rc.dim);
-    attn_prep_token(q, ldq, k, ldk, v, ldv, slot, off, pos0, entry_of, a, pr, kcache, vcache, slot_stride, red);
+    const int64_t t = blockIdx.x;
+    hgrn2_prep_rows(q + t * ldq, f + t * ldf, f_bias, lower, n);
 }
 
 // ---- C: both branches' results into the operand of the one output product.  grid (tokens, left heads + right heads): a CTA of the first
@@ -595,15 +602,25 @@ int launch_causal_conv(const float * u, int64_t ldu, const BatchView & b, int ch
     });
 }
 
-int launch_attn_prep_store(float * q, int64_t ldq, float * k, int64_t ldk, float * v, int64_t ldv, const BatchView & b, const AttnParams & a,
-                           const AttnPrep & pr, float * kcache, float * vcache, int64_t slot_stride, cudaStream_t st) {
-    if (b.n_tokens <= 0) return 0;
+static int dual_prep_launch(const RecPrep & rc, float * q, int64_t ldq, float * k, int64_t ldk, float * v, int64_t ldv, const BatchView & b, const AttnParams & a,
+                            const AttnPrep & pr, float * kcache, float * vcache, int64_t slot_stride, cudaStream_t st) {
     if (a.heads <= 0 || a.kv_heads <= 0 || a.dim <= 0 || a.vdim <= 0 || pr.rot_dims < 0 || pr.rot_dims > a.dim || (pr.rot_dims & 1) ||
         (pr.rot_dims > 0 && !pr.rot_freq) || (pr.v_rot && !pr.v_freq) || (pr.norm == QKN_WHOLE_WEIGHT && (!pr.wq || !pr.wk)))
         return (int) cudaErrorInvalidValue;
+    // the token's rows in shared memory when they fit
+    const size_t floats = (size_t) a.heads * a.dim + (size_t) a.kv_heads * (a.dim + a.vdim) + (rc.kind >= 0 ? 2 * (size_t) rc.qk_heads * rc.dim : 0);
+    const int staged = floats * sizeof(float) <= 160 * 1024;
+    const size_t smem = staged ? floats * sizeof(float) : 0;
+    int e = raise_smem(k_dual_prep_store, smem);
+    if (e) return e;
     return ck_launch([&] {
-        k_attn_prep_store<<<b.n_tokens, 256, 0, st>>>(q, ldq, k, ldk, v, ldv, b.slot, b.off, b.pos0, b.entry_of, a, pr, kcache, vcache, slot_stride);
+        k_dual_prep_store<<<b.n_tokens, 256, smem, st>>>(rc, q, ldq, k, ldk, v, ldv, b.slot, b.off, b.pos0, b.entry_of, a, pr, kcache, vcache, slot_stride, staged);
     });
+}
+int launch_attn_prep_store(float * q, int64_t ldq, float * k, int64_t ldk, float * v, int64_t ldv, const BatchView & b, const AttnParams & a,
+                           const AttnPrep & pr, float * kcache, float * vcache, int64_t slot_stride, cudaStream_t st) {
+    if (b.n_tokens <= 0) return 0;
+    return dual_prep_launch(RecPrep(), q, ldq, k, ldk, v, ldv, b, a, pr, kcache, vcache, slot_stride, st);
 }
 
 int launch_attn_unrotate_gate(const float * o, const BatchView & b, int heads, int vdim, int v_layout, const float * v_freq, const float * gate, int64_t ldg,
@@ -674,17 +691,13 @@ int launch_dual_prep_store(int rec_kind, float * rq, int64_t ldrq, float * rk, i
                            const float * p1, int qk_heads, int r_heads, int r_dim, float * q, int64_t ldq, float * k, int64_t ldk, float * v, int64_t ldv,
                            const BatchView & b, const AttnParams & a, const AttnPrep & pr, float * kcache, float * vcache, int64_t slot_stride, cudaStream_t st) {
     if (b.n_tokens <= 0) return 0;
-    if (a.heads <= 0 || a.kv_heads <= 0 || a.dim <= 0 || a.vdim <= 0 || pr.rot_dims < 0 || pr.rot_dims > a.dim || (pr.rot_dims & 1) ||
-        (pr.rot_dims > 0 && !pr.rot_freq) || (pr.v_rot && !pr.v_freq) || (pr.norm == QKN_WHOLE_WEIGHT && (!pr.wq || !pr.wk)) || rec_kind < 0 || rec_kind > 1 ||
-        !rq || !rk || !p0 || !p1 || qk_heads <= 0 || r_dim <= 0 || (rec_kind == 0 && (!beta || !ra || r_heads <= 0)))
+    if (rec_kind < 0 || rec_kind > 1 || !rq || !rk || !p0 || !p1 || qk_heads <= 0 || r_dim <= 0 || (rec_kind == 0 && (!beta || !ra || r_heads <= 0)))
         return (int) cudaErrorInvalidValue;
     RecPrep rc;
     rc.kind = rec_kind;
     rc.q = rq; rc.ldq = ldrq; rc.k = rk; rc.ldk = ldrk; rc.beta = beta; rc.ldb = ldb; rc.a = ra; rc.lda = lda;
     rc.p0 = p0; rc.p1 = p1; rc.qk_heads = qk_heads; rc.heads = r_heads; rc.dim = r_dim;
-    return ck_launch([&] {
-        k_dual_prep_store<<<b.n_tokens, 256, 0, st>>>(rc, q, ldq, k, ldk, v, ldv, b.slot, b.off, b.pos0, b.entry_of, a, pr, kcache, vcache, slot_stride);
-    });
+    return dual_prep_launch(rc, q, ldq, k, ldk, v, ldv, b, a, pr, kcache, vcache, slot_stride, st);
 }
 
 int launch_dual_post(const float * o, const BatchView & b, int heads, int vdim, int v_layout, const float * v_freq, const float * gate, int64_t ldg, int gate_mode,
