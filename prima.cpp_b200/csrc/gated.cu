@@ -91,9 +91,17 @@ __device__ __forceinline__ void pair_of(int i, int dims, int layout, int & ia, i
 // One CTA per token.  (1) RMS norm over the whole query projection and over the whole key projection with weights; (2) rotation of the
 // leading entries of every query and key head; (3) every head divided by its own root mean square; (4) rotation of the value heads;
 // (5) the K / V rows later tokens can still see go to the cache.  Steps that the design does not have are skipped.
-__device__ __forceinline__ void attn_prep_rows(float * qr, float * kr, float * vr, float fp, const AttnParams & a, const AttnPrep & pr, float * red) {
+// cs: scratch of rot_dims + vdim floats in shared memory: the token's cosines and sines, computed once for all heads
+__device__ __forceinline__ void attn_prep_rows(float * qr, float * kr, float * vr, float fp, const AttnParams & a, const AttnPrep & pr, float * red, float * cs) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int QD = a.heads * a.dim, KD = a.kv_heads * a.dim;
+    const int hq = pr.rot_dims / 2, hv2 = pr.v_rot ? a.vdim / 2 : 0;
+    float * csv = cs + 2 * hq;
+    for (int i = threadIdx.x; i < hq + hv2; i += blockDim.x) {
+        if (i < hq) sincosf(fp * pr.rot_freq[i], &cs[2 * i + 1], &cs[2 * i]);
+        else sincosf(fp * pr.v_freq[i - hq], &csv[2 * (i - hq) + 1], &csv[2 * (i - hq)]);
+    }
+    // the barrier after the whole-projection norm, or the one below, makes the table visible
     if (pr.norm == QKN_WHOLE_WEIGHT) {
         float sq = 0.f, sk = 0.f;
         for (int i = threadIdx.x; i < QD; i += blockDim.x) sq = fmaf(qr[i], qr[i], sq);
@@ -102,8 +110,8 @@ __device__ __forceinline__ void attn_prep_rows(float * qr, float * kr, float * v
         const float ik = 1.f / sqrtf(block_sum(sk, red) / (float) KD + pr.eps);
         for (int i = threadIdx.x; i < QD; i += blockDim.x) qr[i] = qr[i] * iq * pr.wq[i];
         for (int i = threadIdx.x; i < KD; i += blockDim.x) kr[i] = kr[i] * ik * pr.wk[i];
-        __syncthreads();
     }
+    __syncthreads();
     if (pr.rot_dims > 1) {
         const int hp = pr.rot_dims / 2, total = (a.heads + a.kv_heads) * hp;
         for (int j = threadIdx.x; j < total; j += blockDim.x) {
@@ -111,7 +119,9 @@ __device__ __forceinline__ void attn_prep_rows(float * qr, float * kr, float * v
             float * hv = hh < a.heads ? qr + (int64_t) hh * a.dim : kr + (int64_t) (hh - a.heads) * a.dim;
             int ia, ib;
             pair_of(i, pr.rot_dims, pr.rot_layout, ia, ib);
-            turn(hv[ia], hv[ib], fp * pr.rot_freq[i]);
+            const float u = hv[ia], w = hv[ib], c = cs[2 * i], sn = cs[2 * i + 1];
+            hv[ia] = u * c - w * sn;
+            hv[ib] = w * c + u * sn;
         }
         __syncthreads();
     }
@@ -131,7 +141,9 @@ __device__ __forceinline__ void attn_prep_rows(float * qr, float * kr, float * v
             float * hv = vr + (int64_t) hh * a.vdim;
             int ia, ib;
             pair_of(i, 2 * hp, pr.v_layout, ia, ib);
-            turn(hv[ia], hv[ib], fp * pr.v_freq[i]);
+            const float u = hv[ia], w = hv[ib], c = csv[2 * i], sn = csv[2 * i + 1];
+            hv[ia] = u * c - w * sn;
+            hv[ib] = w * c + u * sn;
         }
     }
 }
@@ -189,8 +201,10 @@ __global__ void __launch_bounds__(256) k_dual_prep_store(RecPrep rc, float * __r
     float * gq = q + (int64_t) t * ldq, * gk = k + (int64_t) t * ldk, * gv = v + (int64_t) t * ldv;
     float * grq = rc.kind >= 0 ? rc.q + (int64_t) t * rc.ldq : nullptr, * grk = rc.kind >= 0 ? rc.k + (int64_t) t * rc.ldk : nullptr;
     float * qr = gq, * kr = gk, * vr = gv, * rqr = grq, * rkr = grk;
+    float * cs = sm;                                 // the token's cosines and sines: [rot_dims] for q / k, [vdim] for v
+    float * rows = sm + ((pr.rot_dims + a.vdim + 3) & ~3);
     if (staged) {
-        qr = sm; kr = qr + QD; vr = kr + KD; rqr = vr + VD; rkr = rqr + RQ;
+        qr = rows; kr = qr + QD; vr = kr + KD; rqr = vr + VD; rkr = rqr + RQ;
         for (int i = threadIdx.x; i < QD; i += blockDim.x) qr[i] = gq[i];
         for (int i = threadIdx.x; i < KD; i += blockDim.x) kr[i] = gk[i];
         for (int i = threadIdx.x; i < VD; i += blockDim.x) vr[i] = gv[i];
@@ -199,7 +213,7 @@ __global__ void __launch_bounds__(256) k_dual_prep_store(RecPrep rc, float * __r
     }
     if (rc.kind == 0) delta_prep_rows(rqr, rkr, rc.beta + (int64_t) t * rc.ldb, rc.a + (int64_t) t * rc.lda, rc.p0, rc.p1, rc.qk_heads, rc.heads, rc.dim);
     else if (rc.kind == 1) hgrn2_prep_rows(rqr, rkr, rc.p0, rc.p1, RQ);
-    attn_prep_rows(qr, kr, vr, (float) p, a, pr, red);
+    attn_prep_rows(qr, kr, vr, (float) p, a, pr, red, cs);
     __syncthreads();
     if (staged) {
         for (int i = threadIdx.x; i < QD; i += blockDim.x) gq[i] = qr[i];
@@ -609,8 +623,9 @@ static int dual_prep_launch(const RecPrep & rc, float * q, int64_t ldq, float * 
         return (int) cudaErrorInvalidValue;
     // the token's rows in shared memory when they fit
     const size_t floats = (size_t) a.heads * a.dim + (size_t) a.kv_heads * (a.dim + a.vdim) + (rc.kind >= 0 ? 2 * (size_t) rc.qk_heads * rc.dim : 0);
-    const int staged = floats * sizeof(float) <= 160 * 1024;
-    const size_t smem = staged ? floats * sizeof(float) : 0;
+    const size_t table = (size_t) ((pr.rot_dims + a.vdim + 3) & ~3);   // cosines and sines of the token's position
+    const int staged = (floats + table) * sizeof(float) <= 160 * 1024;
+    const size_t smem = (table + (staged ? floats : 0)) * sizeof(float);
     int e = raise_smem(k_dual_prep_store, smem);
     if (e) return e;
     return ck_launch([&] {
