@@ -247,8 +247,9 @@ PB200_API int pb200_dense(int type, const void * A, int64_t lda, const void * W,
  * Two families share the model object: 0 = one fixed transformer graph over k-quant GGUF weights ("llama", "qwen2":
  * pb200_model_create / pb200_model_load_gguf), 1 = layer list: a configuration file lists the layers, each with a sequence mixer
  * (windowed attention with kept first tokens, a Mamba-2 state-space mixer, linear attention with a fixed decay per head, softmax attention
- * over a low-rank latent) and an optional feed-forward (gated or squared-ReLU, dense or a routed mixture of experts), over dense f32 / bf16
- * weights ("Vamidra", "Mumizen", "Sapudra": pb200_model_create_from_config / pb200_model_load_dir).  pb200_arch_family: -1 for an unknown name. */
+ * over a low-rank latent, or an attention branch beside a gated linear recurrence) and an optional feed-forward (gated or squared-ReLU,
+ * dense or a routed mixture of experts), over dense f32 / bf16
+ * weights ("Vamidra", "Mumizen", "Sapudra", "Zevedra": pb200_model_create_from_config / pb200_model_load_dir).  pb200_arch_family: -1 for an unknown name. */
 PB200_API int          pb200_arch_count(void);
 PB200_API const char * pb200_arch_name(int i);
 PB200_API int          pb200_arch_family(const char * name);
