@@ -49,11 +49,24 @@ def config(layers, width=64, vocab=131, loop=None, mult=0.65, scale=6.0, bigram=
     return c
 
 
-def mixed_config(every_expert=False):
-    # five layers, the middle three run three times.  every_expert: each token uses all experts of a layer, so no score's rounding can send
-    # it elsewhere (long bfloat16 runs)
-    def moe(experts=6, top=2, ff=24):
-        return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": min(experts, 3) if every_expert else experts, "top": min(experts, 3) if every_expert else top}}
+def every_expert(cfg):
+    """The same model with at most three experts per layer, all of them chosen by every token: no score's rounding can send a token
+    elsewhere.  For bfloat16 runs through several layers, where a routing flip early on would move every later row."""
+    c = copy.deepcopy(cfg)
+    for layer in c["layers"]:
+        if layer.get("mlp"):
+            n = min(layer["mlp"]["router"]["experts"], 3)
+            layer["mlp"]["router"] = {"experts": n, "top": n}
+    return c
+
+
+def for_dtype(cfg, dtype):
+    deep = len(R.layer_runs(cfg)) > 1
+    return every_expert(cfg) if dtype == "bfloat16" and deep else cfg
+
+
+def mixed_config():
+    # five layers, the middle three run three times
     return config([par(mlp=moe()), par2(mlp=moe(experts=5, top=1, ff=32)), par(heads=6, kv_heads=1, dim=12, vdim=8, window=11, rot=4, conv=2, r_heads=2, r_kv=1,
                                                                                 r_dim=16, r_vdim=8, r_conv=4),
                    par2(heads=2, kv_heads=2, dim=24, vdim=8, rot=24, r_heads=2, r_dim=12, r_vdim=12, mlp=moe(experts=4, top=3, ff=16)),
@@ -151,6 +164,7 @@ MECHANISMS = {
 @pytest.mark.parametrize("which", sorted(MECHANISMS))
 def test_each_mechanism_alone(pkg, cuda, which, dtype, tol):
     cfg, edits = MECHANISMS[which]()
+    cfg = for_dtype(cfg, dtype)
     bits, W = R.random_weights(cfg, seed=3)
     for name, f in edits.items():
         R.set_weight(bits, W, name, f(W[name]))
@@ -169,7 +183,7 @@ def test_each_mechanism_alone(pkg, cuda, which, dtype, tol):
 
 @pytest.mark.parametrize("dtype,tol", [("float32", F32_TOL), ("bfloat16", BF16_TOL)])
 def test_prompt_and_decoding_agree_with_the_oracle(pkg, cuda, dtype, tol):
-    cfg = mixed_config()
+    cfg = for_dtype(mixed_config(), dtype)
     bits, W = R.random_weights(cfg, seed=5)
     toks = tokens_for(cfg, 90, 2)
     want, _, sure = oracle(cfg, W, toks, dtype)
@@ -348,6 +362,7 @@ def test_the_window_passes_over_decoded_tokens_many_times(pkg, cuda, dtype, tol)
     # windows of 1, 2, 5 and 17 rows: every decoded token overwrites the oldest row of each ring; 150 steps wrap them many times
     cfg = config([par(window=17, mlp=moe()), par(heads=2, kv_heads=2, dim=8, vdim=8, window=1, rot=8), par(heads=2, kv_heads=1, dim=12, vdim=20, window=2, rot=6),
                   par(heads=3, kv_heads=1, dim=8, vdim=8, window=5, rot=8)])
+    cfg = for_dtype(cfg, dtype)
     bits, W = R.random_weights(cfg, seed=13)
     toks = tokens_for(cfg, 170, 5)
     want, _, sure = oracle(cfg, W, toks, dtype)
@@ -388,7 +403,7 @@ def test_first_tokens_of_a_sequence(pkg, cuda):
 
 @pytest.mark.parametrize("dtype,tol", [("float32", F32_TOL), ("bfloat16", BF16_TOL)])
 def test_long_decoding(pkg, cuda, dtype, tol):
-    cfg = mixed_config(every_expert=dtype == "bfloat16")
+    cfg = for_dtype(mixed_config(), dtype)
     bits, W = R.random_weights(cfg, seed=16)
     toks = tokens_for(cfg, 260, 6)
     want, _, sure = oracle(cfg, W, toks, dtype)
@@ -417,7 +432,7 @@ ODD = {
 @pytest.mark.parametrize("dtype,tol", [("float32", F32_TOL), ("bfloat16", BF16_TOL)])
 @pytest.mark.parametrize("which", sorted(ODD))
 def test_other_sizes(pkg, cuda, which, dtype, tol):
-    cfg = ODD[which]()
+    cfg = for_dtype(ODD[which](), dtype)
     bits, W = R.random_weights(cfg, seed=17)
     toks = tokens_for(cfg, 45, 7)
     want, _, sure = oracle(cfg, W, toks, dtype)
