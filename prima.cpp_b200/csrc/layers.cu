@@ -210,6 +210,10 @@ struct LayerList {
     // decode steps replayed as CUDA graphs, one per (entries, wanted rows); the batch's metadata lives at fixed device addresses
     struct StepGraph { cudaGraphExec_t exec = nullptr; int seen = 0; uint64_t launches = 0; };
     std::map<uint64_t, StepGraph> graphs;
+    // a dual mixer's recurrent branch runs on a second stream beside the attention branch (fork after the token preparation, join before the
+    // branches meet); the pair of events is capturable, so a replayed decode graph keeps the two branches side by side
+    cudaStream_t side = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     std::vector<int> rows_tmp;      // logits row of the caller (or -(entry+1) for a greedy row) per wanted row of the last sub-batch
 };
 
@@ -1267,6 +1271,9 @@ void ll_free(pb200_model * m) {
     if (ll->lat_part) cudaFree(ll->lat_part);
     if (ll->tap) cudaFree(ll->tap);
     for (cudaEvent_t e : ll->prof_ev) cudaEventDestroy(e);
+    if (ll->ev_fork) cudaEventDestroy(ll->ev_fork);
+    if (ll->ev_join) cudaEventDestroy(ll->ev_join);
+    if (ll->side) cudaStreamDestroy(ll->side);
     delete ll;
     m->ll = nullptr;
 }
@@ -1610,23 +1617,21 @@ static int mix_dual(pb200_model * m, const BatchView & b, bool prefill, const LR
     else
         CK(launch_dual_prep_store(1, src + d.c_rq, ld, src + d.c_rk, ld, nullptr, 0, nullptr, 0, L.f_bias.data, L.f_lower.data, rp.qk_heads, rp.heads, rp.dim,
                                   src + d.c_q, ld, src + d.c_k, ld, src + d.c_v, ld, b, a, pr, kc, vc, ll.slot_floats, st));
-    AttnIO io;
-    io.q = src + d.c_q; io.ldq = ld;
-    io.k = src + d.c_k; io.ldk = ld;
-    io.v = src + d.c_v; io.ldv = ld;
-    io.k_row = (int64_t) a.kv_heads * a.dim; io.v_row = (int64_t) a.kv_heads * a.vdim;
     const bool sum = d.join == JOIN_SCALED_SUM;
-    const bool post = d.v_rot || sum;   // the head results are turned back, gated and scaled into their place by a kernel of their own
-    if (!post) { io.gate = ll.big + d.c_g; io.ldg = C; io.gate_mode = d.gate_mode; }
-    void * att_out = post ? (void *) ll.big2 : ll.act;
-    const int att_type = post ? T_F32 : ct;
-    if (prefill) CK(launch_attn_prefill_io(io, b, a, att_out, att_type, st));
-    else CK(launch_attn_decode_io(io, b, a, kc, vc, ll.slot_floats, att_out, att_type, st, ll.lat_part));
-    const int64_t ldo = sum ? OD + RV : OD;
-    if (post && !sum)
-        CK(launch_attn_unrotate_gate(ll.big2, b, a.heads, a.vdim, d.rot_layout, d.v_rot ? L.vrot_freq.data : nullptr, ll.big + d.c_g, C, d.gate_mode, 1.f, ll.act,
-                                     ldo, ct, st));
-    // ---- recurrent branch ----
+    // ---- recurrent branch: on the second stream beside the attention branch, unless every launch is being timed ----
+    static const bool one_stream = getenv("PB200_ONE_STREAM") != nullptr;   // A/B: both branches in a row on one stream
+    const bool forked = !ll.prof_on && !one_stream;
+    cudaStream_t rst = st;
+    if (forked) {
+        if (!ll.side) {
+            CK(cudaStreamCreateWithFlags(&ll.side, cudaStreamNonBlocking));
+            CK(cudaEventCreateWithFlags(&ll.ev_fork, cudaEventDisableTiming));
+            CK(cudaEventCreateWithFlags(&ll.ev_join, cudaEventDisableTiming));
+        }
+        rst = ll.side;
+        CK(cudaEventRecord(ll.ev_fork, st));
+        CK(cudaStreamWaitEvent(rst, ll.ev_fork, 0));
+    }
     CAT(CAT_SCAN);
     GatedLinIO gi;
     gi.q = src + d.c_rq; gi.ldq = ld;
@@ -1638,7 +1643,32 @@ static int mix_dual(pb200_model * m, const BatchView & b, bool prefill, const LR
     } else {
         gi.decay = src + d.c_rk; gi.ldd = ld;
     }
-    CK(launch_gated_linattn(gi, b, rp, rec_state, ll.slot_floats, ll.yssm, st));
+    CK(launch_gated_linattn(gi, b, rp, rec_state, ll.slot_floats, ll.yssm, rst));
+    if (!sum) {   // every head by its own root mean square with the weight all heads share -> operand of the branch's own output product
+        CAT(CAT_NORM);
+        CK(launch_norm_gate(ll.yssm, d.rec == REC_DELTA ? ll.big + d.c_rg : nullptr, C, rp.heads, L.onorm.data, d.rec == REC_DELTA ? 1 : -1, ll.eps, ll.act2, ct, T, RV,
+                            rst, RV, 1.f));
+    }
+    if (forked) CK(cudaEventRecord(ll.ev_join, rst));
+    // ---- attention branch ----
+    CAT(CAT_ATTN);
+    AttnIO io;
+    io.q = src + d.c_q; io.ldq = ld;
+    io.k = src + d.c_k; io.ldk = ld;
+    io.v = src + d.c_v; io.ldv = ld;
+    io.k_row = (int64_t) a.kv_heads * a.dim; io.v_row = (int64_t) a.kv_heads * a.vdim;
+    const bool post = d.v_rot || sum;   // the head results are turned back, gated and scaled into their place by a kernel of their own
+    if (!post) { io.gate = ll.big + d.c_g; io.ldg = C; io.gate_mode = d.gate_mode; }
+    void * att_out = post ? (void *) ll.big2 : ll.act;
+    const int att_type = post ? T_F32 : ct;
+    if (prefill) CK(launch_attn_prefill_io(io, b, a, att_out, att_type, st));
+    else CK(launch_attn_decode_io(io, b, a, kc, vc, ll.slot_floats, att_out, att_type, st, ll.lat_part));
+    const int64_t ldo = sum ? OD + RV : OD;
+    if (post && !sum)
+        CK(launch_attn_unrotate_gate(ll.big2, b, a.heads, a.vdim, d.rot_layout, d.v_rot ? L.vrot_freq.data : nullptr, ll.big + d.c_g, C, d.gate_mode, 1.f, ll.act,
+                                     ldo, ct, st));
+    // ---- the branches meet ----
+    if (forked) CK(cudaStreamWaitEvent(st, ll.ev_join, 0));
     CAT(CAT_NORM);
     if (sum) {
         // attention heads turned back and gated; recurrence heads by their own root mean square, the weight all heads share, the SiLU gate; both
@@ -1649,8 +1679,6 @@ static int mix_dual(pb200_model * m, const BatchView & b, bool prefill, const LR
         CAT(CAT_DENSE);
         return launch_dense(ct, ll.act, ldo, L.out.data, ldo, x, W, T, W, (int) ldo, nullptr, x, W, mult, st);
     }
-    CK(launch_norm_gate(ll.yssm, d.rec == REC_DELTA ? ll.big + d.c_rg : nullptr, C, rp.heads, L.onorm.data, d.rec == REC_DELTA ? 1 : -1, ll.eps, ll.act2, ct, T, RV,
-                        st, RV, 1.f));
     CAT(CAT_DENSE);
     CK(launch_dense(ct, ll.act, OD, L.out.data, OD, ll.big4, 2 * W, T, W, OD, nullptr, nullptr, 0, 1.f, st));
     CK(launch_dense(ct, ll.act2, RV, L.out_r.data, RV, ll.big4 + W, 2 * W, T, W, RV, nullptr, nullptr, 0, 1.f, st));
