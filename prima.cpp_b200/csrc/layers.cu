@@ -1611,7 +1611,14 @@ static int mix_dual(pb200_model * m, const BatchView & b, bool prefill, const LR
     pr.rot_dims = d.rot_dims; pr.rot_layout = d.rot_layout; pr.rot_freq = L.rot_freq.data;
     pr.v_rot = d.v_rot; pr.v_layout = d.rot_layout; pr.v_freq = d.v_rot ? L.vrot_freq.data : nullptr;
     // one launch prepares both branches: the recurrence's inputs (unit vectors, gates, decays), then the attention inputs and the cache store
-    if (d.rec == REC_DELTA)
+    // (PB200_DUAL_UNFUSED: the same steps as the single ops the layers were brought up on, one launch each; for A/B runs and tests)
+    static const bool unfused = getenv("PB200_DUAL_UNFUSED") != nullptr;
+    if (unfused) {
+        if (d.rec == REC_DELTA)
+            CK(launch_delta_prep(src + d.c_rq, ld, src + d.c_rk, ld, ll.big + d.c_rb, C, ll.big + d.c_ra, C, L.A_log.data, L.dt_bias.data, rp.qk_heads, rp.heads, rp.dim, T, st));
+        else CK(launch_hgrn2_prep(src + d.c_rq, ld, src + d.c_rk, ld, L.f_bias.data, L.f_lower.data, rp.qk_heads * rp.dim, T, st));
+        CK(launch_attn_prep_store(src + d.c_q, ld, src + d.c_k, ld, src + d.c_v, ld, b, a, pr, kc, vc, ll.slot_floats, st));
+    } else if (d.rec == REC_DELTA)
         CK(launch_dual_prep_store(0, src + d.c_rq, ld, src + d.c_rk, ld, ll.big + d.c_rb, C, ll.big + d.c_ra, C, L.A_log.data, L.dt_bias.data, rp.qk_heads, rp.heads,
                                   rp.dim, src + d.c_q, ld, src + d.c_k, ld, src + d.c_v, ld, b, a, pr, kc, vc, ll.slot_floats, st));
     else
@@ -1670,6 +1677,14 @@ static int mix_dual(pb200_model * m, const BatchView & b, bool prefill, const LR
     // ---- the branches meet ----
     if (forked) CK(cudaStreamWaitEvent(st, ll.ev_join, 0));
     CAT(CAT_NORM);
+    if (sum && unfused) {
+        CK(launch_attn_unrotate_gate(ll.big2, b, a.heads, a.vdim, d.rot_layout, d.v_rot ? L.vrot_freq.data : nullptr, ll.big + d.c_g, C, d.gate_mode, d.left_scale,
+                                     ll.act, ldo, ct, st));
+        CK(launch_norm_gate(ll.yssm, d.rec == REC_DELTA ? ll.big + d.c_rg : nullptr, C, rp.heads, L.onorm.data, d.rec == REC_DELTA ? 1 : -1, ll.eps,
+                            (uint8_t *) ll.act + (size_t) OD * esize(ct), ct, T, RV, st, ldo, d.right_scale));
+        CAT(CAT_DENSE);
+        return launch_dense(ct, ll.act, ldo, L.out.data, ldo, x, W, T, W, (int) ldo, nullptr, x, W, mult, st);
+    }
     if (sum) {
         // attention heads turned back and gated; recurrence heads by their own root mean square, the weight all heads share, the SiLU gate; both
         // with their branch's factor, side by side as the operand of the one output product

@@ -517,3 +517,34 @@ def test_directory_loader_and_trace_replay(pkg, cuda, tmp_path):
     g1 = np.fromfile(out / "1.f32", dtype="<f4").reshape(2, -1)
     check(g0, np.stack([wa[0], wa[18], wb[6]]), F32_TOL)
     check(g1, np.stack([wa[19], wb[7]]), F32_TOL)
+
+
+def test_fused_and_single_step_kernels_agree(pkg, cuda, tmp_path):
+    # the mixer's fused launches (preparation of both branches, both results into the output product's operand) against the same steps as
+    # single kernels, one launch each (PB200_DUAL_UNFUSED), through the command-line replay: a prompt of two requests, then decoded tokens
+    cfg = mixed_config()
+    bits, W = R.random_weights(cfg, seed=22)
+    d = tmp_path / "model"
+    R.write_model_dir(str(d), cfg, bits)
+    a, b = tokens_for(cfg, 40, 6), tokens_for(cfg, 9, 7)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:36], "want": list(range(36))}, {"id": "b", "tokens": b[:5], "want": [0, 4]}], "end": []}]
+    for k in range(4):
+        steps.append({"step": k + 1, "entries": [{"id": "a", "tokens": [a[36 + k]], "want": [0]}, {"id": "b", "tokens": [b[5 + k]], "want": [0]}], "end": ["a", "b"] if k == 3 else []})
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    rows = {}
+    for mode in ("fused", "single"):
+        env = dict(os.environ)
+        env.pop("PB200_DUAL_UNFUSED", None)
+        if mode == "single":
+            env["PB200_DUAL_UNFUSED"] = "1"
+        out = tmp_path / mode
+        p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(d), "--dtype", "float32", "--out", str(out), "--max-tokens", "64"],
+                           input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600, env=env)
+        assert p.returncode == 0, p.stderr[-2000:]
+        rows[mode] = np.concatenate([np.fromfile(out / f"{k}.f32", dtype="<f4").reshape(-1, cfg["vocab"]) for k in range(5)])
+    wa, _ = R.forward(cfg, W, a)
+    wb, _ = R.forward(cfg, W, b)
+    want = np.concatenate([wa[:36], wb[[0, 4]]] + [np.stack([wa[36 + k], wb[5 + k]]) for k in range(4)])
+    check(rows["fused"], want, F32_TOL)
+    check(rows["single"], want, F32_TOL)
+    assert np.abs(rows["fused"] - rows["single"]).max() < 2e-5 * np.abs(want).max()
