@@ -1241,10 +1241,10 @@ int ll_finalize(pb200_model * m) {
         off = (off + 3) / 4 * 4;
     }
     ll.slot_floats = std::max<int64_t>(off, 4);
-    if (ll.n_seq <= 0) {   // as many slots as 8 GiB of state (or a third of the free device memory, if that is more) hold, between 4 and 256
+    if (ll.n_seq <= 0) {   // as many slots as 8 GiB of state (or an eighth of the free device memory, if that is more) hold, between 4 and 256
         size_t mem_free = 0, mem_total = 0;
         if (cudaMemGetInfo(&mem_free, &mem_total) != cudaSuccess) mem_free = 0;
-        const int64_t fit = std::max<int64_t>(8ll << 30, (int64_t) (mem_free / 3)) / (ll.slot_floats * 4);
+        const int64_t fit = std::max<int64_t>(8ll << 30, (int64_t) (mem_free / 8)) / (ll.slot_floats * 4);
         ll.n_seq = (int) std::min<int64_t>(256, std::max<int64_t>(4, fit));
     }
     CK(m->alloc((void **) &ll.state, (size_t) ll.slot_floats * 4 * (size_t) ll.n_seq));
