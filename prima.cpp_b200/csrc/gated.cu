@@ -26,7 +26,7 @@ __global__ void k_embed_bigram(const WT * __restrict__ table, const WT * __restr
     const int e = entry_of[t];
     const int tok = tokens[t];
     const int pv = t == off[e] ? prev[e] : tokens[t - 1];
-    const int64_t brow = pv < 0 ? bg.buckets : ((int64_t) pv * bg.mul_prev + (int64_t) tok * bg.mul_cur) % bg.buckets;
+    const int64_t brow = (pv < 0 || bg.buckets <= 0) ? bg.buckets : ((int64_t) pv * bg.mul_prev + (int64_t) tok * bg.mul_cur) % bg.buckets;
     const WT * er = table + (int64_t) tok * width;
     const WT * br = bigram ? bigram + brow * width : nullptr;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
